@@ -1,0 +1,169 @@
+"""TEST INFRASTRUCTURE — NOT THE PRODUCT.
+
+numpy front-end to ``liboracle.so`` (the plain-C CPU restatement in
+``t81_oracle.c``).  Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU
+legs of ``bench.py`` may import this package; the shipped library never does.
+Each wrapper names the reference lines its C function follows in
+``t81_oracle.h``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+_i64 = ctypes.c_int64
+_f32 = ctypes.c_float
+_p = ctypes.c_void_p
+
+
+def build(force: bool = False) -> str:
+    """Compile ``liboracle.so`` (and, where the reference sources are present,
+    ``_ref``) through the Makefile beside this file."""
+    if force and os.path.exists(_LIB_PATH):
+        os.remove(_LIB_PATH)
+    subprocess.run(["make", "-C", _HERE, "oracle"], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        src = os.path.join(_HERE, "t81_oracle.c")
+        if not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+            build()
+        L = ctypes.CDLL(_LIB_PATH)
+        L.t81o_quantize_to_trits.argtypes = [_p, ctypes.c_size_t, _f32, _p]
+        L.t81o_pack_trits_rowwise.argtypes = [_p, _i64, _i64, _p]
+        L.t81o_pack_trits_columnwise.argtypes = [_p, _i64, _i64, _p]
+        L.t81o_pack_dense_matrix.argtypes = [_p, _i64, _i64, _i64, _f32, _p]
+        L.t81o_pack_dense_matrix_absmean.argtypes = [_p, _i64, _i64, _i64, _f32, _p, _p]
+        L.t81o_unpack_packed_limbs.argtypes = [_p, _i64, _i64, _i64, _p]
+        L.t81o_unpack_packed_limbs.restype = ctypes.c_int
+        L.t81o_gemm_limb.argtypes = [_p, _p, _p, _i64, _i64, _i64, _f32, _f32]
+        L.t81o_gemm_trit.argtypes = [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _f32]
+        L.t81o_linear_forward.argtypes = [_p, _p, _p, _p, _p, _i64, _i64, _i64]
+        L.t81o_num_threads.restype = ctypes.c_int
+        L.t81o_set_num_threads.argtypes = [ctypes.c_int]
+        for name in ("t81o_quantize_to_trits", "t81o_pack_trits_rowwise", "t81o_pack_trits_columnwise",
+                     "t81o_pack_dense_matrix", "t81o_pack_dense_matrix_absmean", "t81o_gemm_limb",
+                     "t81o_gemm_trit", "t81o_linear_forward", "t81o_set_num_threads"):
+            getattr(L, name).restype = None
+        _lib = L
+    return _lib
+
+
+def _ptr(a: np.ndarray | None):
+    return None if a is None else a.ctypes.data_as(_p)
+
+
+def _f32c(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def set_num_threads(n: int) -> None:
+    lib().t81o_set_num_threads(int(n))
+
+
+def num_threads() -> int:
+    return lib().t81o_num_threads()
+
+
+def k_limbs(cols: int) -> int:
+    return (cols + 47) // 48
+
+
+def quantize_to_trits(values, threshold: float = 0.5) -> np.ndarray:
+    src = _f32c(values)
+    out = np.empty(src.shape, dtype=np.int8)
+    lib().t81o_quantize_to_trits(_ptr(src), src.size, threshold, _ptr(out))
+    return out
+
+
+def pack_trits_rowwise(trits) -> np.ndarray:
+    t = np.ascontiguousarray(trits, dtype=np.int8)
+    rows, cols = t.shape
+    out = np.empty((rows, k_limbs(cols), 16), dtype=np.uint8)
+    lib().t81o_pack_trits_rowwise(_ptr(t), rows, cols, _ptr(out))
+    return out
+
+
+def pack_trits_columnwise(trits) -> np.ndarray:
+    t = np.ascontiguousarray(trits, dtype=np.int8)
+    k, cols = t.shape
+    out = np.empty((k_limbs(k), cols, 16), dtype=np.uint8)
+    lib().t81o_pack_trits_columnwise(_ptr(t), k, cols, _ptr(out))
+    return out
+
+
+def pack_dense_matrix(w, threshold: float = 0.5) -> np.ndarray:
+    w = _f32c(w)
+    rows, cols = w.shape
+    out = np.empty((rows, k_limbs(cols), 16), dtype=np.uint8)
+    lib().t81o_pack_dense_matrix(_ptr(w), rows, cols, cols, threshold, _ptr(out))
+    return out
+
+
+def pack_dense_matrix_absmean(w, threshold: float = 0.45):
+    w = _f32c(w)
+    rows, cols = w.shape
+    out = np.empty((rows, k_limbs(cols), 16), dtype=np.uint8)
+    scale = np.empty(rows, dtype=np.float32)
+    lib().t81o_pack_dense_matrix_absmean(_ptr(w), rows, cols, cols, threshold, _ptr(out), _ptr(scale))
+    return out, scale
+
+
+def unpack_packed_limbs(packed, rows: int, cols: int) -> np.ndarray:
+    p = np.ascontiguousarray(packed, dtype=np.uint8)
+    kl = p.size // (16 * rows) if rows else 0
+    out = np.zeros((rows, cols), dtype=np.int8)
+    if lib().t81o_unpack_packed_limbs(_ptr(p), rows, kl, cols, _ptr(out)) != 0:
+        raise ValueError("packed limb byte out of range (> 26)")
+    return out
+
+
+def gemm_limb(A, B, C, M: int, N: int, K: int, alpha: float = 1.0, beta: float = 0.0) -> np.ndarray:
+    """In-place on a float32 copy of C, which is returned."""
+    A = np.ascontiguousarray(A, dtype=np.uint8)
+    B = np.ascontiguousarray(B, dtype=np.uint8)
+    C = np.array(C, dtype=np.float32, order="C", copy=True).reshape(M, N)
+    lib().t81o_gemm_limb(_ptr(A), _ptr(B), _ptr(C), M, N, K // 48, alpha, beta)
+    return C
+
+
+def gemm_trit(A, B, C, M: int, N: int, K: int, alpha: float = 1.0, beta: float = 0.0,
+              b_is_nk: bool = False) -> np.ndarray:
+    """A packed (M, ceil(K/48), 16); B dense (K, N) — or (N, K) with
+    ``b_is_nk`` — returns (M, N), or (N, M) with ``b_is_nk`` (the Linear layout)."""
+    A = np.ascontiguousarray(A, dtype=np.uint8)
+    B = _f32c(B)
+    if b_is_nk:
+        C = (np.zeros((N, M), np.float32) if C is None
+             else np.array(C, dtype=np.float32, order="C", copy=True).reshape(N, M))
+        lib().t81o_gemm_trit(_ptr(A), _ptr(B), _ptr(C), M, N, K, 1, K, 1, M, alpha, beta)
+    else:
+        C = (np.zeros((M, N), np.float32) if C is None
+             else np.array(C, dtype=np.float32, order="C", copy=True).reshape(M, N))
+        lib().t81o_gemm_trit(_ptr(A), _ptr(B), _ptr(C), M, N, K, N, 1, N, 1, alpha, beta)
+    return C
+
+
+def linear_forward(W_packed, row_scale, bias, x, in_features: int) -> np.ndarray:
+    W = np.ascontiguousarray(W_packed, dtype=np.uint8)
+    out_features = W.shape[0]
+    x = _f32c(x).reshape(-1, in_features)
+    rs = None if row_scale is None else _f32c(row_scale)
+    b = None if bias is None else _f32c(bias)
+    y = np.empty((x.shape[0], out_features), dtype=np.float32)
+    lib().t81o_linear_forward(_ptr(W), _ptr(rs), _ptr(b), _ptr(x), _ptr(y), x.shape[0],
+                              out_features, in_features)
+    return y
