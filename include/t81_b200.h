@@ -1,0 +1,154 @@
+/*
+ * t81_b200.h — C ABI of libt81_b200.so: the packed balanced-ternary matmul path
+ * of t81lib on NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Plain C types only.  Every function returns T81B200_OK (0) or a negative
+ *     T81B200_E* code; nothing throws, traps or aborts.  A description of the
+ *     last failure on the calling thread is available from t81b200_last_error().
+ *   - Unless a name ends in _host, every data pointer is a DEVICE pointer that
+ *     the caller owns and lends for the duration of the call.  Work is queued on
+ *     `stream` (a cudaStream_t passed as void*; NULL = the legacy default
+ *     stream) and the call returns without synchronising.
+ *   - Nothing is allocated inside these calls, except where a comment says so;
+ *     scratch memory is passed in (`workspace`), sized by the matching
+ *     *_workspace_bytes query.
+ *   - There is no CPU fallback: without a usable device the calls fail with
+ *     T81B200_ENODEVICE.
+ *
+ * Packed layout (the bit-exact contract, t81lib include/t81/core/limb.hpp:95-235,708
+ * and include/t81/core/detail/lut.hpp:13-49): a limb is 16 bytes holding 48 balanced
+ * trits; byte i is the tryte of trits 3i, 3i+1, 3i+2, byte = t0 + 3*t1 + 9*t2 + 13
+ * (0..26, zero tryte 13).  A (rows, cols) matrix is packed row-wise into
+ * (rows, ceil(cols/48), 16) bytes with zero tail trits
+ * (python/bindings.cpp:470-516, t81/torch/__init__.py:68-80).
+ */
+#ifndef T81_B200_H
+#define T81_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define T81B200_API __attribute__((visibility("default")))
+#else
+#define T81B200_API
+#endif
+
+#define T81B200_TRITS_PER_LIMB 48
+#define T81B200_BYTES_PER_LIMB 16
+
+enum {
+    T81B200_OK = 0,
+    T81B200_EINVAL = -1,     /* bad dimension, pointer, enum or size relation   */
+    T81B200_ENODEVICE = -2,  /* no CUDA device / driver, or not an sm_100 part   */
+    T81B200_ECUDA = -3,      /* a CUDA runtime call or launch failed             */
+    T81B200_EWORKSPACE = -4, /* workspace missing or smaller than required       */
+    T81B200_EALIGN = -5,     /* pointer alignment the kernel needs is not met    */
+    T81B200_ELIMIT = -6      /* size beyond a stated fixed maximum               */
+};
+
+enum { T81B200_F32 = 0, T81B200_BF16 = 1, T81B200_F16 = 2 };
+
+/* Quantiser rule. FIXED is the reference rule (python/bindings.cpp:405-414,
+ * t81/torch/__init__.py:44-50).  ABSMEAN divides each row by the mean of |w| of
+ * that row first and returns that mean as the row's scale; the reference has no
+ * such rule, it is shaped after quantize_row_tq1_0 (src/t81/core/gguf_quants.h:116-144)
+ * with the mean in place of the absmax. */
+enum { T81B200_RULE_FIXED = 0, T81B200_RULE_ABSMEAN = 1 };
+
+/* Operand layout of the dense side of t81b200_gemm_trit.
+ *   KN: B is (K, N) row-major and C is (M, N) row-major — the argument order of
+ *       t81::linalg::gemm_ternary (include/t81/linalg/gemm.hpp:68-77).
+ *   NK: B is (N, K) row-major (activations, one token per row) and C is (N, M)
+ *       row-major (one token per row) — the layout of TernaryTensor.matmul_input
+ *       and nn.Linear (t81/torch/__init__.py:241-246, t81/nn/linear.py:53-70). */
+enum { T81B200_LAYOUT_KN = 0, T81B200_LAYOUT_NK = 1 };
+
+/* 1 when a CUDA device of compute capability 10.x is present and usable.
+ * Stands in for t81::linalg::detail::cuda_available()
+ * (declared include/t81/linalg/gemm_gpu.hpp:68, never defined by the reference). */
+T81B200_API int t81b200_device_available(void);
+
+/* Text of the last error raised on this thread ("" if none). */
+T81B200_API const char *t81b200_last_error(void);
+
+/* Library version string. */
+T81B200_API const char *t81b200_version(void);
+
+/* Threshold quantise + pack, one pass on the device.
+ * Replaces pack_dense_matrix (python/bindings.cpp:460-517),
+ * TernaryTensor.from_float / update_from_float (t81/torch/__init__.py:214-239)
+ * and the Metal kernels quantize_trits_kernel / pack_dense_matrix_kernel
+ * (src/linalg/pack_kernel.metal:29-76).
+ *   w         (rows, cols) of w_dtype, row stride `ld` elements
+ *   threshold compared in fp32, inclusive on both sides; must be in [0, 1].  (The pybind
+ *             entry points reject 0, TernaryTensor clamps to [0, 0.9999]; at exactly 0 the
+ *             negative compare wins, as in t81/torch/__init__.py:44-50.)
+ *   rule      T81B200_RULE_*
+ *   packed    out, rows*ceil(cols/48)*16 bytes
+ *   row_scale out, rows floats; required for ABSMEAN, ignored (may be NULL) for FIXED */
+T81B200_API int t81b200_quantize_pack(const void *w, int w_dtype, int64_t rows, int64_t cols, int64_t ld,
+                          float threshold, int rule, uint8_t *packed, float *row_scale,
+                          void *stream);
+
+/* Elementwise threshold quantiser; replaces quantize_to_trits
+ * (python/bindings.cpp:416-445) and TernaryTensor's _quantize_tensor. */
+T81B200_API int t81b200_quantize_trits(const float *src, int64_t n, float threshold, int8_t *dst,
+                           void *stream);
+
+/* Inverse of the packer; replaces unpack_packed_limbs (python/bindings.cpp:640-686)
+ * and _limbs_to_trits (t81/torch/__init__.py:100-112).
+ *   packed (rows, k_limbs, 16) bytes; trits out (rows, cols) int8, cols <= 48*k_limbs
+ *   bad_bytes: optional device int, incremented once per byte > 26 met (such a
+ *   byte decodes as a zero tryte; the reference's limb::from_bytes rejects it). */
+T81B200_API int t81b200_unpack(const uint8_t *packed, int64_t rows, int64_t k_limbs, int64_t cols,
+                   int8_t *trits, int *bad_bytes, void *stream);
+
+/* LIMB mode — the literal semantics of t81::linalg::gemm_ternary
+ * (include/t81/linalg/gemm.hpp:68-77; CPU kernel src/linalg/gemm_cpu.cpp:8-71;
+ * the CUDA entry it replaces: cuda_gemm_ternary, src/linalg/gemm_cuda.cu:284-341):
+ * C = alpha * value(A) * value(B) + beta * C, value() the 48-trit integer a limb
+ * encodes, accumulated in fp64.  A (M, k_limbs) limbs, B (k_limbs, N) limbs,
+ * C (M, N) fp32, read and written. */
+T81B200_API int t81b200_gemm_limb(const uint8_t *A, const uint8_t *B, float *C, int64_t M, int64_t N,
+                      int64_t k_limbs, float alpha, float beta, void *stream);
+
+/* Same, with HOST pointers (what the span API of gemm_ternary hands over).
+ * Copies in, runs, copies C back and synchronises.  Allocates device staging
+ * buffers on first use and when sizes grow. */
+T81B200_API int t81b200_gemm_limb_host(const uint8_t *A, const uint8_t *B, float *C, int64_t M, int64_t N,
+                           int64_t k_limbs, float alpha, float beta);
+
+/* TRIT mode — packed ternary weights times dense activations:
+ *   C = alpha * diag(row_scale) * T(A) * B + bias + beta * C
+ * with T(A)[m][k] in {-1,0,+1} unpacked from A's limbs and fp32 accumulation.
+ * This is the contraction behind TernaryTensor.matmul_input
+ * (t81/torch/__init__.py:241-276) and t81.nn.Linear's eval forward
+ * (t81/nn/linear.py:42-70).
+ *   A          (M, ceil(K/48)) limbs, M = output features
+ *   row_scale  M floats or NULL (= 1)
+ *   B          dense, K x N logical, b_dtype, layout per `layout`, leading dim ldb elements
+ *   bias       M floats or NULL
+ *   C          c_dtype, layout per `layout`, leading dim ldc elements; read only if beta != 0
+ *   M, N, K    output features, tokens, contraction length (K need not be a multiple of 48;
+ *              trits at positions >= K are ignored)
+ * Token counts up to 16 with NK layout run the HBM-bound streaming kernel, larger
+ * ones the tcgen05 tensor-core kernel.  `workspace` must hold at least
+ * t81b200_gemm_trit_workspace_bytes(...) bytes (0 is possible: then NULL is fine). */
+T81B200_API int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const void *B, int b_dtype,
+                      int layout, int64_t ldb, const float *bias, void *C, int c_dtype,
+                      int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta,
+                      void *workspace, size_t workspace_bytes, void *stream);
+
+T81B200_API size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int c_dtype, int64_t M,
+                                         int64_t N, int64_t K);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T81_B200_H */

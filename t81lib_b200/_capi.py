@@ -1,0 +1,85 @@
+"""ctypes binding of ``libt81_b200.so`` (declared in ``include/t81_b200.h``).
+
+The library is the only compute path: if it is missing or cannot be loaded the
+import of this module fails, and if no B200 is present every call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libt81_b200.so")
+
+OK, EINVAL, ENODEVICE, ECUDA, EWORKSPACE, EALIGN, ELIMIT = 0, -1, -2, -3, -4, -5, -6
+F32, BF16, F16 = 0, 1, 2
+RULE_FIXED, RULE_ABSMEAN = 0, 1
+LAYOUT_KN, LAYOUT_NK = 0, 1
+
+EXPORTS = (
+    "t81b200_device_available", "t81b200_last_error", "t81b200_version", "t81b200_quantize_pack",
+    "t81b200_quantize_trits", "t81b200_unpack", "t81b200_gemm_limb", "t81b200_gemm_limb_host",
+    "t81b200_gemm_trit", "t81b200_gemm_trit_workspace_bytes",
+)
+
+
+class T81B200Error(RuntimeError):
+    """A CUDA-side failure reported by the library (ECUDA, ENODEVICE, ...)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"t81_b200 error {code}: {message}")
+        self.code = code
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -m t81lib_b200.build` "
+            "(there is no fallback implementation)")
+    lib = ctypes.CDLL(LIB_PATH)
+    i64, f32, vp, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int
+    lib.t81b200_device_available.restype = ci
+    lib.t81b200_last_error.restype = ctypes.c_char_p
+    lib.t81b200_version.restype = ctypes.c_char_p
+    lib.t81b200_quantize_pack.argtypes = [vp, ci, i64, i64, i64, f32, ci, vp, vp, vp]
+    lib.t81b200_quantize_trits.argtypes = [vp, i64, f32, vp, vp]
+    lib.t81b200_unpack.argtypes = [vp, i64, i64, i64, vp, vp, vp]
+    lib.t81b200_gemm_limb.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32, vp]
+    lib.t81b200_gemm_limb_host.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32]
+    lib.t81b200_gemm_trit.argtypes = [vp, vp, vp, ci, ci, i64, vp, vp, ci, i64, i64, i64, i64, f32, f32,
+                                      vp, ctypes.c_size_t, vp]
+    lib.t81b200_gemm_trit_workspace_bytes.argtypes = [ci, ci, ci, i64, i64, i64]
+    lib.t81b200_gemm_trit_workspace_bytes.restype = ctypes.c_size_t
+    for name in EXPORTS:
+        fn = getattr(lib, name)
+        if fn.restype is ctypes.c_int and name not in ("t81b200_device_available",):
+            fn.restype = ci
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return lib.t81b200_last_error().decode()
+
+
+def check(code: int) -> None:
+    """Map a return code to the exception the reference raises for that failure:
+    argument problems are ``ValueError`` (pybind's value_error / std::invalid_argument),
+    runtime failures are ``RuntimeError``."""
+    if code == OK:
+        return
+    msg = last_error()
+    if code in (EINVAL, EALIGN, ELIMIT, EWORKSPACE):
+        raise ValueError(msg)
+    raise T81B200Error(code, msg)
+
+
+def device_available() -> bool:
+    return bool(lib.t81b200_device_available())
+
+
+def version() -> str:
+    return lib.t81b200_version().decode()

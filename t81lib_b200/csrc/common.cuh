@@ -1,0 +1,152 @@
+// Shared device helpers and host-side error plumbing for libt81_b200.so (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/t81_b200.h"
+
+namespace t81b200 {
+
+// ---- host: error reporting ------------------------------------------------
+
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);
+int check_device();  // T81B200_OK or T81B200_ENODEVICE (cached per process)
+int sm_count();      // multiprocessors of the current device (cached per device)
+
+#define T81_CUDA_TRY(expr)                                                              \
+    do {                                                                                \
+        cudaError_t err__ = (expr);                                                     \
+        if (err__ != cudaSuccess)                                                       \
+            return ::t81b200::fail(T81B200_ECUDA, "%s failed: %s", #expr,               \
+                                   cudaGetErrorString(err__));                          \
+    } while (0)
+
+#define T81_LAUNCH_CHECK(name)                                                          \
+    do {                                                                                \
+        cudaError_t err__ = cudaGetLastError();                                         \
+        if (err__ != cudaSuccess)                                                       \
+            return ::t81b200::fail(T81B200_ECUDA, "launch of %s failed: %s", name,      \
+                                   cudaGetErrorString(err__));                          \
+    } while (0)
+
+// ---- device: tryte codec ---------------------------------------------------
+// byte = t0 + 3*t1 + 9*t2 + 13  with t in {-1,0,+1}   (zero tryte = 13).
+
+constexpr uint32_t kZeroTryteWord = 0x0D0D0D0Du;
+
+// Scalar decode of one tryte byte into digits d = t + 1 in {0,1,2}.  Bytes above
+// 26 are treated as the zero tryte.
+__device__ __forceinline__ void tryte_digits(uint32_t b, int &d0, int &d1, int &d2) {
+    b = b > 26u ? 13u : b;
+    d2 = (int)((b * 57u) >> 9);  // b / 9 for b < 27
+    const uint32_t r = b - 9u * (uint32_t)d2;
+    d1 = (int)((r * 11u) >> 5);  // r / 3 for r < 9
+    d0 = (int)(r - 3u * (uint32_t)d1);
+}
+
+// Packed decode: two tryte bytes -> their six trits as exact bf16 values.
+//
+// The two bytes are first placed in the mantissas of two bf16 lanes
+// (0x4300 | b  ==  128 + b), then base-3 digits are peeled off with packed bf16
+// FMAs whose single rounding does the floor():
+//   v  = b - 13                      balanced value of the tryte, -13..13
+//   Q  = RN(v * (57/512) + 130)      = 130 + t2          (ulp is 1 in [128,256))
+//   t2 = Q - 130
+//   r  = v - 9*t2                    -4..4
+//   P  = RN(r * (171/512) + 130)     = 130 + t1
+//   t1 = P - 130
+//   t0 = r - 3*t1
+// Every intermediate is an integer below 256 or lands on the magic grid, so each
+// step is exact; the 27 byte values are checked exhaustively by the test suite.
+struct TrytePairTrits {
+    __nv_bfloat162 t0, t1, t2;  // .x from the first byte, .y from the second
+};
+
+__device__ __forceinline__ __nv_bfloat162 bf162_from_bits(uint32_t u) {
+    __nv_bfloat162 r;
+    *reinterpret_cast<uint32_t *>(&r) = u;
+    return r;
+}
+__device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 v) {
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+__device__ __forceinline__ TrytePairTrits decode_tryte_pair(uint32_t x128) {
+    // x128: lanes hold 128 + byte (bit pattern 0x4300 | byte).
+    const __nv_bfloat162 kM141 = bf162_from_bits(0xC30DC30Du);  // -141
+    const __nv_bfloat162 kNinth = bf162_from_bits(0x3DE43DE4u); // 57/512
+    const __nv_bfloat162 kThird = bf162_from_bits(0x3EAB3EABu); // 171/512
+    const __nv_bfloat162 k130 = bf162_from_bits(0x43024302u);   // 130
+    const __nv_bfloat162 kM130 = bf162_from_bits(0xC302C302u);  // -130
+    const __nv_bfloat162 kM9 = bf162_from_bits(0xC110C110u);    // -9
+    const __nv_bfloat162 kM3 = bf162_from_bits(0xC040C040u);    // -3
+    TrytePairTrits o;
+    const __nv_bfloat162 v = __hadd2(bf162_from_bits(x128), kM141);
+    const __nv_bfloat162 q = __hfma2(v, kNinth, k130);
+    o.t2 = __hadd2(q, kM130);
+    const __nv_bfloat162 r = __hfma2(o.t2, kM9, v);
+    const __nv_bfloat162 p = __hfma2(r, kThird, k130);
+    o.t1 = __hadd2(p, kM130);
+    o.t0 = __hfma2(o.t1, kM3, r);
+    return o;
+}
+
+// Bytes (2p, 2p+1) of a 4-byte word as 128+byte bf16 lanes.
+__device__ __forceinline__ uint32_t tryte_pair_lo(uint32_t w) {
+    return __byte_perm(w, 0x43434343u, 0x4140);
+}
+__device__ __forceinline__ uint32_t tryte_pair_hi(uint32_t w) {
+    return __byte_perm(w, 0x43434343u, 0x4342);
+}
+
+// Decode a whole limb (4 words = 16 trytes) into 24 packed registers.
+// Register 3*p + i holds digit i of bytes 2p (low half) and 2p+1 (high half),
+// i.e. trits 6p + i and 6p + 3 + i of the limb.
+__device__ __forceinline__ void decode_limb(const uint4 &limb, uint32_t (&out)[24]) {
+    const uint32_t w[4] = {limb.x, limb.y, limb.z, limb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const TrytePairTrits a = decode_tryte_pair(tryte_pair_lo(w[i]));
+        const TrytePairTrits b = decode_tryte_pair(tryte_pair_hi(w[i]));
+        out[6 * i + 0] = bf162_bits(a.t0);
+        out[6 * i + 1] = bf162_bits(a.t1);
+        out[6 * i + 2] = bf162_bits(a.t2);
+        out[6 * i + 3] = bf162_bits(b.t0);
+        out[6 * i + 4] = bf162_bits(b.t1);
+        out[6 * i + 5] = bf162_bits(b.t2);
+    }
+}
+
+// Position inside a limb of the trit held by (register r, half h) of decode_limb.
+__host__ __device__ __forceinline__ int decoded_trit_index(int r, int h) {
+    return 6 * (r / 3) + 3 * h + (r % 3);
+}
+
+// ---- device: dtype loads/stores ---------------------------------------------
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+}
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_float<__half>(float v) {
+    return __float2half_rn(v);
+}
+
+__host__ __device__ inline size_t dtype_size(int dtype) { return dtype == T81B200_F32 ? 4 : 2; }
+
+}  // namespace t81b200

@@ -1,0 +1,339 @@
+// Decode-shaped TRIT-mode kernel: packed ternary weights (M rows) times up to 16
+// activation rows (tokens).  The weight stream is the only large operand, so the
+// kernel is HBM-bound by design: each lane pulls whole 16-byte limbs with 128-bit
+// loads, expands them to exact bf16 {-1,0,+1} in registers with packed bf16 FMAs
+// (common.cuh), and feeds them straight into mma.sync m16n8k16 as the A fragment —
+// the expanded weights never touch shared or global memory.
+//
+// Work split
+//   grid.x : row tiles of 128*RG rows (8 warps, RG groups of 16 rows per warp)
+//   grid.y : S slices of the contraction, S = cluster size (1..8).  The S CTAs of
+//            a cluster hold partial sums for the same rows; they are combined
+//            through distributed shared memory in rank order (deterministic), so
+//            no global scratch and no atomics are involved.
+//   lane (g = lane/4, t = lane%4) of a warp loads, for each chunk of 4 limbs,
+//   limb 4c+t of rows g and g+8.  The order of the contraction index inside an
+//   MMA is free as long as both operands agree, so the activations are staged in
+//   shared memory already permuted into the register order decode_limb produces.
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+namespace t81b200 {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kPrefetch = 4;  // chunks of 4 limbs in flight per lane
+
+struct GemvParams {
+    const uint8_t *A;       // (M, kl, 16)
+    const void *X;          // (ntok, K) row-major, ldx elements
+    const float *row_scale; // M or null
+    const float *bias;      // M or null
+    void *C;                // (ntok, M) row-major, ldc elements
+    int64_t M, K, kl, ldx, ldc;
+    int ntok;
+    int limbs_per_slice;    // multiple of 4
+    int row_groups;         // RG
+    float alpha, beta;
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// Stage the activations of limbs [L0, L0+nl) for `ntok` tokens into shared memory in
+// decode_limb register order.  Plane 0 holds bf16(x); plane 1 (PLANES == 2) holds
+// bf16(x - plane0), so that plane0 + plane1 carries 16 mantissa bits of an fp32 input.
+template <typename XT, int PLANES>
+__device__ __forceinline__ void stage_activations(const GemvParams &p, int L0, int nl, uint32_t *xs,
+                                                  int tok_stride, int plane_stride) {
+    const XT *X = static_cast<const XT *>(p.X);
+    const bool vec_ok = sizeof(XT) == 2 && (reinterpret_cast<uintptr_t>(X) % 16 == 0) && (p.ldx % 8 == 0);
+    for (int item = threadIdx.x; item < p.ntok * nl; item += kThreads) {
+        const int tok = item / nl, l = item - tok * nl;
+        const int64_t k0 = (int64_t)(L0 + l) * 48;
+        uint32_t *dst = xs + tok * tok_stride + l * 24;
+        if constexpr (PLANES == 1) {
+            if (vec_ok && k0 + 48 <= p.K) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(X + (int64_t)tok * p.ldx + k0);
+                uint32_t n[24];
+#pragma unroll
+                for (int q = 0; q < 6; ++q) {
+                    const uint4 v = __ldg(src + q);
+                    n[4 * q] = v.x; n[4 * q + 1] = v.y; n[4 * q + 2] = v.z; n[4 * q + 3] = v.w;
+                }
+                uint32_t o[24];
+#pragma unroll
+                for (int pr = 0; pr < 8; ++pr) {
+                    o[3 * pr + 0] = __byte_perm(n[3 * pr], n[3 * pr + 1], 0x7610);
+                    o[3 * pr + 1] = __byte_perm(n[3 * pr], n[3 * pr + 2], 0x5432);
+                    o[3 * pr + 2] = __byte_perm(n[3 * pr + 1], n[3 * pr + 2], 0x7610);
+                }
+#pragma unroll
+                for (int q = 0; q < 6; ++q)
+                    reinterpret_cast<uint4 *>(dst)[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                continue;
+            }
+        }
+        for (int r = 0; r < 24; ++r) {
+            float e[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int64_t k = k0 + decoded_trit_index(r, h);
+                e[h] = k < p.K ? to_float<XT>(X[(int64_t)tok * p.ldx + k]) : 0.0f;
+            }
+            const uint32_t hi = pack_bf16(e[0], e[1]);
+            dst[r] = hi;
+            if constexpr (PLANES == 2) {
+                const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162 *>(&hi);
+                dst[plane_stride + r] = pack_bf16(e[0] - __low2float(hv), e[1] - __high2float(hv));
+            }
+        }
+    }
+}
+
+template <typename CT>
+__device__ __forceinline__ void store_out(const GemvParams &p, int64_t row, int tok, float acc) {
+    if (row >= p.M || tok >= p.ntok) return;
+    float v = acc * p.alpha;
+    if (p.row_scale) v *= p.row_scale[row];
+    if (p.bias) v += p.bias[row];
+    CT *c = static_cast<CT *>(p.C) + (int64_t)tok * p.ldc + row;
+    if (p.beta != 0.0f) v += p.beta * to_float<CT>(*c);
+    *c = from_float<CT>(v);
+}
+
+template <typename XT> struct Planes { static constexpr int value = 2; };
+template <> struct Planes<__nv_bfloat16> { static constexpr int value = 1; };
+
+template <typename XT, typename CT, int TOKB>
+__global__ void __launch_bounds__(kThreads, 2) gemv_trit_kernel(const GemvParams p) {
+    constexpr int PLANES = Planes<XT>::value;
+    extern __shared__ __align__(16) uint32_t smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int slices = (int)cluster.num_blocks();
+    const int slice = (int)cluster.block_rank();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
+    const int L0 = slice * p.limbs_per_slice;
+    int nl = kl4 - L0;
+    nl = nl < 0 ? 0 : (nl > p.limbs_per_slice ? p.limbs_per_slice : nl);
+
+    // shared memory: [activations: PLANES x ntok x tok_stride] [partials: rows x 8*TOKB floats]
+    const int tok_stride = p.limbs_per_slice * 24 + 4;  // +16 bytes: conflict-free 128-bit reads
+    const int plane_stride = p.ntok * tok_stride;
+    uint32_t *xs = smem;
+    float *part = reinterpret_cast<float *>(smem + PLANES * plane_stride);
+    constexpr int kTokPad = 8 * TOKB;
+    const int rows_per_cta = kWarps * 16 * p.row_groups;
+
+    stage_activations<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride);
+    __syncthreads();
+
+    const int64_t cta_row0 = (int64_t)blockIdx.x * rows_per_cta;
+    const int chunks = nl >> 2;
+    const uint4 zero_limb = make_uint4(kZeroTryteWord, kZeroTryteWord, kZeroTryteWord, kZeroTryteWord);
+
+    for (int rg = 0; rg < p.row_groups; ++rg) {
+        const int64_t r0 = cta_row0 + (int64_t)(rg * kWarps + warp) * 16;
+        if (r0 >= p.M) continue;  // nothing to add; the reduction never stores rows >= M
+        int64_t ra = r0 + g, rb = r0 + g + 8;
+        ra = ra < p.M ? ra : p.M - 1;
+        rb = rb < p.M ? rb : p.M - 1;
+        const uint4 *pa = reinterpret_cast<const uint4 *>(p.A) + ra * p.kl + L0 + t;
+        const uint4 *pb = reinterpret_cast<const uint4 *>(p.A) + rb * p.kl + L0 + t;
+
+        float acc[TOKB][4];
+#pragma unroll
+        for (int b = 0; b < TOKB; ++b) acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f;
+
+        uint4 qa[kPrefetch], qb[kPrefetch];
+#pragma unroll
+        for (int s = 0; s < kPrefetch; ++s) {
+            const bool in = s < chunks && (L0 + 4 * s + t) < p.kl;
+            qa[s] = in ? ldg_stream(pa + 4 * s) : zero_limb;
+            qb[s] = in ? ldg_stream(pb + 4 * s) : zero_limb;
+        }
+
+        for (int c0 = 0; c0 < chunks; c0 += kPrefetch) {
+#pragma unroll
+            for (int s = 0; s < kPrefetch; ++s) {
+                const int c = c0 + s;
+                if (c < chunks) {
+                    uint32_t wa[24], wb[24];
+                    decode_limb(qa[s], wa);
+                    decode_limb(qb[s], wb);
+                    const int cn = c + kPrefetch;
+                    const bool in = cn < chunks && (L0 + 4 * cn + t) < p.kl;
+                    qa[s] = in ? ldg_stream(pa + 4 * cn) : zero_limb;
+                    qb[s] = in ? ldg_stream(pb + 4 * cn) : zero_limb;
+#pragma unroll
+                    for (int b = 0; b < TOKB; ++b) {
+                        const int tok = 8 * b + g;
+#pragma unroll
+                        for (int pl = 0; pl < PLANES; ++pl) {
+                            const uint4 *xv = reinterpret_cast<const uint4 *>(
+                                xs + pl * plane_stride + tok * tok_stride + (4 * c + t) * 24);
+#pragma unroll
+                            for (int q = 0; q < 6; ++q) {
+                                uint4 x = make_uint4(0, 0, 0, 0);
+                                if (tok < p.ntok) x = xv[q];
+                                mma_bf16_16816(acc[b], wa[4 * q], wb[4 * q], wa[4 * q + 1], wb[4 * q + 1], x.x, x.y);
+                                mma_bf16_16816(acc[b], wa[4 * q + 2], wb[4 * q + 2], wa[4 * q + 3], wb[4 * q + 3], x.z, x.w);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+
+        // acc[b][0]: (row g, token 8b+2t), [1]: (row g, 8b+2t+1), [2]: (row g+8, 8b+2t), [3]: (row g+8, 8b+2t+1)
+        if (slices == 1) {
+#pragma unroll
+            for (int b = 0; b < TOKB; ++b) {
+                store_out<CT>(p, r0 + g, 8 * b + 2 * t, acc[b][0]);
+                store_out<CT>(p, r0 + g, 8 * b + 2 * t + 1, acc[b][1]);
+                store_out<CT>(p, r0 + g + 8, 8 * b + 2 * t, acc[b][2]);
+                store_out<CT>(p, r0 + g + 8, 8 * b + 2 * t + 1, acc[b][3]);
+            }
+        } else {
+            const int lr = (rg * kWarps + warp) * 16;  // local row of this warp's group
+#pragma unroll
+            for (int b = 0; b < TOKB; ++b) {
+                float *d0 = part + (lr + g) * kTokPad + 8 * b + 2 * t;
+                float *d1 = part + (lr + g + 8) * kTokPad + 8 * b + 2 * t;
+                *reinterpret_cast<float2 *>(d0) = make_float2(acc[b][0], acc[b][1]);
+                *reinterpret_cast<float2 *>(d1) = make_float2(acc[b][2], acc[b][3]);
+            }
+        }
+    }
+
+    if (slices > 1) {
+        cluster.sync();
+        // CTA `slice` finishes rows [slice*span, (slice+1)*span) of the tile, summing ranks 0..S-1 in order.
+        const int span = (rows_per_cta + slices - 1) / slices;
+        const int lo = slice * span;
+        const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
+        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += kThreads) {
+            float s = 0.0f;
+            for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
+            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+        }
+        cluster.sync();  // peers may still be reading this CTA's partials
+    }
+}
+
+template <typename XT, typename CT, int TOKB>
+int launch(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) {
+    auto kern = gemv_trit_kernel<XT, CT, TOKB>;
+    if (smem_bytes > 48 * 1024)
+        T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    const int rows_per_cta = kWarps * 16 * p.row_groups;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((p.M + rows_per_cta - 1) / rows_per_cta), (unsigned)slices, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)slices;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    T81_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+    return T81B200_OK;
+}
+
+template <typename XT, typename CT>
+int launch_tokb(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) {
+    return p.ntok > 8 ? launch<XT, CT, 2>(p, slices, smem_bytes, st) : launch<XT, CT, 1>(p, slices, smem_bytes, st);
+}
+
+template <typename XT>
+int launch_ct(const GemvParams &p, int c_dtype, int slices, size_t smem_bytes, cudaStream_t st) {
+    switch (c_dtype) {
+        case T81B200_F32: return launch_tokb<XT, float>(p, slices, smem_bytes, st);
+        case T81B200_BF16: return launch_tokb<XT, __nv_bfloat16>(p, slices, smem_bytes, st);
+        case T81B200_F16: return launch_tokb<XT, __half>(p, slices, smem_bytes, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
+}
+
+}  // namespace
+
+// Host entry used by the dispatcher in capi.cu.  NK layout, ntok in 1..16, A 16-byte aligned.
+int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, int x_dtype, int64_t ldx,
+                     const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int ntok, int64_t K,
+                     float alpha, float beta, cudaStream_t st) {
+    GemvParams p;
+    p.A = A; p.X = X; p.row_scale = row_scale; p.bias = bias; p.C = C;
+    p.M = M; p.K = K; p.kl = (K + 47) / 48; p.ldx = ldx; p.ldc = ldc; p.ntok = ntok;
+    p.alpha = alpha; p.beta = beta;
+    const int planes = x_dtype == T81B200_BF16 ? 1 : 2;
+    const int tokpad = ntok > 8 ? 16 : 8;
+    const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
+
+    // Choose rows per CTA and the number of K slices so that about three waves of CTAs
+    // exist and a slice's activations fit in shared memory next to a second CTA.
+    const int sms = sm_count();
+    const size_t smem_budget = 100 * 1024;
+    int best_rg = 1, best_s = 1;
+    double best_score = -1.0;
+    for (int rg = 1; rg <= 4; rg *= 2) {
+        const int rows_per_cta = kWarps * 16 * rg;
+        const int64_t row_tiles = (M + rows_per_cta - 1) / rows_per_cta;
+        for (int s = 1; s <= 8; s *= 2) {
+            int lps = (kl4 / 4 + s - 1) / s * 4;
+            if (lps < 4) lps = 4;
+            if ((int64_t)(s - 1) * lps >= kl4 && s > 1) continue;  // an empty slice
+            const size_t smem = (size_t)planes * ntok * (lps * 24 + 4) * 4 + (s > 1 ? (size_t)rows_per_cta * tokpad * 4 : 0);
+            if (smem > smem_budget) continue;
+            const double ctas = (double)row_tiles * s;
+            // prefer >= 2 CTAs per SM; among those, the largest tile (least staging per row)
+            double score = ctas >= 2.0 * sms ? 1000.0 + rows_per_cta * (double)lps : ctas;
+            if (score > best_score) { best_score = score; best_rg = rg; best_s = s; }
+        }
+    }
+    if (best_score < 0.0)
+        return fail(T81B200_ELIMIT, "gemm_trit: K=%lld too large for the streaming kernel", (long long)K);
+    p.row_groups = best_rg;
+    p.limbs_per_slice = (kl4 / 4 + best_s - 1) / best_s * 4;
+    if (p.limbs_per_slice < 4) p.limbs_per_slice = 4;
+    const int rows_per_cta = kWarps * 16 * best_rg;
+    const size_t smem = (size_t)planes * ntok * (p.limbs_per_slice * 24 + 4) * 4 +
+                        (best_s > 1 ? (size_t)rows_per_cta * tokpad * 4 : 0);
+    switch (x_dtype) {
+        case T81B200_BF16: return launch_ct<__nv_bfloat16>(p, c_dtype, best_s, smem, st);
+        case T81B200_F32: return launch_ct<float>(p, c_dtype, best_s, smem, st);
+        case T81B200_F16: return launch_ct<__half>(p, c_dtype, best_s, smem, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
+}
+
+}  // namespace t81b200

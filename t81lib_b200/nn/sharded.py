@@ -1,0 +1,96 @@
+"""Column-sharded ternary Linear: output features are split across the ranks of a
+process group (one process per GPU); each rank quantises, packs and multiplies
+only its slice of rows, and one all-gather over NVLink assembles the result.
+
+Row-wise packing and per-row scales make a shard self-contained: the packed
+bytes of rank r's slice equal rows [r*out/R, (r+1)*out/R) of the unsharded
+packed matrix, byte for byte.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+
+def shard_bounds(out_features: int, world_size: int, rank: int) -> tuple[int, int]:
+    """Rows [lo, hi) owned by ``rank``.  ``out_features`` must divide evenly so
+    that every rank contributes an equal, contiguous chunk to the all-gather."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} is not in a group of {world_size}")
+    if out_features % world_size != 0:
+        raise ValueError(f"out_features ({out_features}) must be divisible by the group size ({world_size})")
+    per = out_features // world_size
+    return rank * per, (rank + 1) * per
+
+
+def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather (tokens, out/R) slices into (tokens, out).  One collective; the
+    rank-major gather buffer is re-viewed token-major with a single copy."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return local
+    tokens, per = local.shape
+    gathered = torch.empty((world, tokens, per), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
+    if tokens == 1:
+        return gathered.reshape(1, world * per)
+    return gathered.permute(1, 0, 2).reshape(tokens, world * per)
+
+
+class ShardedLinear(nn.Module):
+    """Eval-only ternary Linear whose rows are sharded over ``group``.
+
+    Built either from the full float weight (each rank keeps its slice) or from
+    an ``nn.Linear`` via ``from_linear``.  Activations are replicated."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, threshold: float = 0.45,
+                 rule: str = "fixed", group=None, rank: Optional[int] = None, world_size: Optional[int] = None,
+                 matmul=None, quantize=None):
+        super().__init__()
+        if weight.ndim != 2:
+            raise ValueError("t81.trit tensors currently only support 2D matrices")
+        self.group = group
+        self.world_size = world_size if world_size is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
+        self.out_features, self.in_features = weight.shape
+        lo, hi = shard_bounds(self.out_features, self.world_size, self.rank)
+        self.rows = (lo, hi)
+        self.ternary_threshold = threshold
+        self.ternary_rule = rule
+        # `quantize` / `matmul` are injection points for host-side tests of the sharding
+        # logic; the defaults are the device kernels.
+        if quantize is None:
+            from .. import torch as t81_torch
+            self.ternary_weight = t81_torch.TernaryTensor.from_float(weight[lo:hi].detach(), threshold=threshold, rule=rule)
+            self._matmul = lambda x, b: self.ternary_weight.matmul_input(x, bias=b)
+        else:
+            self.ternary_weight = quantize(weight[lo:hi].detach(), threshold, rule)
+            self._matmul = matmul
+        self.bias = None if bias is None else bias[lo:hi].detach().clone()
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, **kwargs) -> "ShardedLinear":
+        threshold = kwargs.pop("threshold", getattr(linear, "ternary_threshold", 0.45))
+        return cls(linear.weight, linear.bias, threshold=threshold, **kwargs)
+
+    def forward_local(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's (tokens, out/R) slice, no communication."""
+        if x.ndim != 2:
+            raise ValueError("t81.nn.Linear expects 2D or 3D inputs")
+        bias = self.bias
+        if bias is not None and bias.device != x.device:
+            bias = self.bias = bias.to(x.device)
+        return self._matmul(x, bias)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.ndim == 3:
+            b, s, f = x.shape
+            return self.forward(x.reshape(b * s, f)).reshape(b, s, -1)
+        local = self.forward_local(x)
+        if self.world_size == 1:
+            return local
+        return gather_columns(local, self.group)

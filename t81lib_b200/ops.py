@@ -1,0 +1,172 @@
+"""Tensor-level entry points over the C ABI.
+
+Every function takes CUDA tensors, queues work on torch's current stream and
+returns CUDA tensors.  torch is used for device memory and streams only; all
+arithmetic happens in ``libt81_b200.so``.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _capi
+
+TRITS_PER_LIMB = 48
+BYTES_PER_LIMB = 16
+
+_DTYPES = {torch.float32: _capi.F32, torch.bfloat16: _capi.BF16, torch.float16: _capi.F16}
+_RULES = {"fixed": _capi.RULE_FIXED, "absmean": _capi.RULE_ABSMEAN}
+
+
+def k_limbs(cols: int) -> int:
+    return (cols + TRITS_PER_LIMB - 1) // TRITS_PER_LIMB
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+
+
+def _dtype_code(t: torch.Tensor, name: str) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise ValueError(f"{name} must be float32, bfloat16 or float16, got {t.dtype}") from None
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Per-device scratch buffer, grown on demand and reused by later calls on the
+    same stream order."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def quantize_pack(w: torch.Tensor, threshold: float = 0.5, rule: str = "fixed",
+                  out: Optional[torch.Tensor] = None,
+                  row_scale_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Threshold-quantise a 2-D weight and pack it row-wise into limbs.
+
+    Returns ``(packed uint8 (rows, k_limbs, 16), row_scale float32 (rows,) or None)``.
+    """
+    if w.ndim != 2:
+        raise ValueError("pack_dense_matrix expects a 2D array")
+    _require_cuda(w, "w")
+    if rule not in _RULES:
+        raise ValueError(f"unknown quantiser rule {rule!r}")
+    if w.stride(1) != 1 and w.numel() > 0:
+        w = w.contiguous()
+    rows, cols = w.shape
+    kl = k_limbs(cols)
+    with torch.cuda.device(w.device):
+        packed = out if out is not None else torch.empty((rows, kl, 16), dtype=torch.uint8, device=w.device)
+        if out is not None and (out.numel() != rows * kl * 16 or out.dtype != torch.uint8 or not out.is_contiguous()):
+            raise ValueError("packed output buffer has the wrong size")
+        scale = None
+        if rule == "absmean":
+            scale = row_scale_out if row_scale_out is not None else torch.empty(rows, dtype=torch.float32, device=w.device)
+        ld = w.stride(0) if rows > 1 else max(cols, 1)
+        _capi.check(_capi.lib.t81b200_quantize_pack(
+            _ptr(w), _dtype_code(w, "w"), rows, cols, max(ld, cols), float(threshold), _RULES[rule],
+            _ptr(packed), _ptr(scale), _stream(w.device)))
+    return packed, scale
+
+
+def quantize_trits(values: torch.Tensor, threshold: float = 0.5) -> torch.Tensor:
+    _require_cuda(values, "values")
+    src = values.to(torch.float32).contiguous()
+    out = torch.empty(src.shape, dtype=torch.int8, device=src.device)
+    with torch.cuda.device(src.device):
+        _capi.check(_capi.lib.t81b200_quantize_trits(_ptr(src), src.numel(), float(threshold), _ptr(out),
+                                                     _stream(src.device)))
+    return out
+
+
+def unpack(packed: torch.Tensor, rows: int, cols: int, count_bad: bool = False):
+    """Packed limbs -> int8 trits (rows, cols).  With ``count_bad`` also returns the
+    number of bytes above 26 that were met."""
+    _require_cuda(packed, "packed")
+    packed = packed.contiguous()
+    kl = packed.numel() // (16 * rows) if rows else 0
+    trits = torch.empty((rows, cols), dtype=torch.int8, device=packed.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=packed.device) if count_bad else None
+    with torch.cuda.device(packed.device):
+        _capi.check(_capi.lib.t81b200_unpack(_ptr(packed), rows, kl, cols, _ptr(trits), _ptr(bad),
+                                             _stream(packed.device)))
+    if count_bad:
+        return trits, int(bad.item())
+    return trits
+
+
+def gemm_limb(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, M: int, N: int, K: int,
+              alpha: float = 1.0, beta: float = 0.0) -> None:
+    """LIMB mode, in place on C (float32 (M, N) CUDA)."""
+    for t, name in ((A, "A"), (B, "B"), (C, "C")):
+        _require_cuda(t, name)
+    with torch.cuda.device(C.device):
+        _capi.check(_capi.lib.t81b200_gemm_limb(_ptr(A), _ptr(B), _ptr(C), M, N, K // TRITS_PER_LIMB,
+                                                float(alpha), float(beta), _stream(C.device)))
+
+
+def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: str,
+              row_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+              C: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
+              out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """TRIT mode.  ``layout="kn"``: B is (K, N), result (M, N).  ``layout="nk"``:
+    B is (N, K) (one token per row), result (N, M)."""
+    _require_cuda(packed, "packed")
+    _require_cuda(B, "B")
+    if B.ndim != 2:
+        raise ValueError("gemm_trit expects a 2D dense operand")
+    if B.stride(1) != 1 and B.numel() > 0:
+        B = B.contiguous()
+    if layout == "kn":
+        if B.shape[0] != K:
+            raise ValueError("rhs dimension does not match ternary weight width")
+        N = B.shape[1]
+        c_shape, code = (M, N), _capi.LAYOUT_KN
+    elif layout == "nk":
+        if B.shape[1] != K:
+            raise ValueError("rhs dimension does not match ternary weight width")
+        N = B.shape[0]
+        c_shape, code = (N, M), _capi.LAYOUT_NK
+    else:
+        raise ValueError(f"unknown layout {layout!r}")
+    if C is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 needs C")
+        C = torch.empty(c_shape, dtype=out_dtype or B.dtype, device=B.device)
+    else:
+        _require_cuda(C, "C")
+        if tuple(C.shape) != c_shape or C.stride(1) != 1:
+            raise ValueError(f"C must have shape {c_shape} with unit inner stride")
+    b_code, c_code = _dtype_code(B, "B"), _dtype_code(C, "C")
+    ldb = B.stride(0) if B.shape[0] > 1 else max(B.shape[1], 1)
+    ldc = C.stride(0) if C.shape[0] > 1 else max(C.shape[1], 1)
+    rs = None if row_scale is None else row_scale.to(device=B.device, dtype=torch.float32).contiguous()
+    bs = None if bias is None else bias.to(device=B.device, dtype=torch.float32).contiguous()
+    with torch.cuda.device(B.device):
+        need = _capi.lib.t81b200_gemm_trit_workspace_bytes(b_code, code, c_code, M, N, K)
+        ws = _workspace(B.device, need)
+        _capi.check(_capi.lib.t81b200_gemm_trit(
+            _ptr(packed), _ptr(rs), _ptr(B), b_code, code, ldb, _ptr(bs), _ptr(C), c_code, ldc,
+            M, N, K, float(alpha), float(beta), _ptr(ws), 0 if ws is None else ws.numel(), _stream(B.device)))
+    return C

@@ -1,0 +1,417 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and with the
+fixtures generated from the reference.  Integer/byte results must be bit-exact;
+float results are compared at the tolerances written next to each check."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev(lib_built):
+    from t81lib_b200 import _capi
+    assert _capi.device_available(), _capi.last_error()
+    return torch.device("cuda", 0)
+
+
+def cuda(a, dev, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    return t if dtype is None else t.to(dtype)
+
+
+def rel_err(got, want):
+    """Largest error relative to the RMS of the expected result: outputs are sums of
+    cancelling terms, so single elements may sit near zero."""
+    want = np.asarray(want, np.float64)
+    scale = np.sqrt(np.mean(want ** 2)) + 1e-30
+    return float(np.max(np.abs(np.asarray(got, np.float64) - want)) / scale)
+
+
+# ---------------------------------------------------------------- quantise + pack
+
+
+def test_pack_fixed_bit_exact_with_reference_fixtures(dev, golden):
+    from t81lib_b200 import ops
+    g = golden("pack_fixed.npz")
+    w = cuda(g["w"], dev)
+    for name, thr in (("t045", 0.45), ("t050", 0.5), ("t100", 1.0), ("t001", 0.01)):
+        packed, scale = ops.quantize_pack(w, thr, "fixed")
+        assert scale is None
+        assert np.array_equal(packed.cpu().numpy(), g[f"packed_{name}"]), name
+        assert np.array_equal(ops.quantize_trits(w, thr).cpu().numpy(), g[f"trits_{name}"]), name
+    # threshold 0 follows the reference's Python layer (negative compare wins on zeros)
+    packed, _ = ops.quantize_pack(w, 0.0, "fixed")
+    assert np.array_equal(packed.cpu().numpy(), g["from_float_t000"])
+    for cols in (1, 47, 48, 49, 96, 145):
+        packed, _ = ops.quantize_pack(cuda(g[f"w_c{cols}"], dev), 0.45, "fixed")
+        assert np.array_equal(packed.cpu().numpy(), g[f"packed_c{cols}"]), cols
+    trits = ops.unpack(cuda(g["packed_t045"], dev), 64, 100)
+    assert np.array_equal(trits.cpu().numpy(), g["unpacked_t045"])
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 50), (64, 100), (7, 4096), (5, 4100), (3, 5000), (2, 16384),
+                                       (2, 20000), (300, 257)])
+@pytest.mark.parametrize("rule", ["fixed", "absmean"])
+def test_pack_matches_oracle(dev, rows, cols, rule):
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(rows * 100003 + cols)
+    sigma = 0.5 if rule == "fixed" else 0.02
+    w = rng.normal(0, sigma, (rows, cols)).astype(np.float32)
+    if rows > 2:
+        w[2] = 0.0  # an all-zero row: scale 0, all trits 0
+    packed, scale = ops.quantize_pack(cuda(w, dev), 0.45, rule)
+    if rule == "fixed":
+        want = oracle.pack_dense_matrix(w, 0.45)
+    else:
+        want, want_scale = oracle.pack_dense_matrix_absmean(w, 0.45)
+        assert np.array_equal(scale.cpu().numpy(), want_scale)  # bit-exact: same summation order
+    assert np.array_equal(packed.cpu().numpy(), want)
+
+
+def test_pack_strided_unaligned_and_half_inputs(dev):
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(11)
+    big = rng.normal(0, 0.5, (40, 301)).astype(np.float32)
+    t = cuda(big, dev)
+    view = t[:, 1:290]  # row stride 301, base offset 4 bytes: scalar-load path
+    packed, scale = ops.quantize_pack(view, 0.45, "absmean")
+    want, want_scale = oracle.pack_dense_matrix_absmean(big[:, 1:290], 0.45)
+    assert np.array_equal(packed.cpu().numpy(), want) and np.array_equal(scale.cpu().numpy(), want_scale)
+    for dt in (torch.bfloat16, torch.float16):
+        h = t.to(dt)
+        packed, scale = ops.quantize_pack(h, 0.45, "absmean")
+        want, want_scale = oracle.pack_dense_matrix_absmean(h.float().cpu().numpy(), 0.45)
+        assert np.array_equal(packed.cpu().numpy(), want) and np.array_equal(scale.cpu().numpy(), want_scale)
+
+
+def test_pack_config2_full_size_properties(dev):
+    """BASELINE config 2 at full size: 4096x4096 N(0, 0.02^2), threshold 0.45."""
+    from t81lib_b200 import ops
+    gen = torch.Generator(device="cpu").manual_seed(2)
+    w = (torch.randn(4096, 4096, generator=gen) * 0.02)
+    wd = w.to(dev)
+    # rule "fixed": 0.45 is 22 sigma, every trit is 0, every byte the zero tryte
+    packed, _ = ops.quantize_pack(wd, 0.45, "fixed")
+    assert packed.shape == (4096, 86, 16) and bool((packed == 13).all())
+    # rule "absmean": bit-exact against the oracle, and a round trip through unpack
+    packed, scale = ops.quantize_pack(wd, 0.45, "absmean")
+    want, want_scale = oracle.pack_dense_matrix_absmean(w.numpy(), 0.45)
+    assert np.array_equal(packed.cpu().numpy(), want)
+    assert np.array_equal(scale.cpu().numpy(), want_scale)
+    trits = ops.unpack(packed, 4096, 4096)
+    again, _ = ops.quantize_pack(trits.float(), 0.5, "fixed")  # idempotence: trits re-pack to the same bytes
+    assert torch.equal(again, packed)
+    assert int(packed.max()) <= 26
+
+
+def test_unpack_counts_invalid_bytes(dev):
+    from t81lib_b200 import ops, t81lib
+    p = np.full((2, 3, 16), 13, np.uint8)
+    p[1, 2, 7] = 200
+    trits, bad = ops.unpack(cuda(p, dev), 2, 144, count_bad=True)
+    assert bad == 1 and not trits.any()
+    with pytest.raises(ValueError):
+        t81lib.unpack_packed_limbs(p, 2, 144)
+
+
+# ---------------------------------------------------------------- tryte decode used by the matmul kernels
+
+
+def test_every_tryte_value_decodes_exactly_in_the_matmul_kernels(dev):
+    """All 27 byte values at all 16 byte positions, each trit probed by a one-hot
+    activation: the streaming kernel must reproduce the unpacked trits exactly."""
+    from t81lib_b200 import ops
+    rows, K = 27 * 16, 48
+    p = np.full((rows, 1, 16), 13, np.uint8)
+    for v in range(27):
+        for pos in range(16):
+            p[v * 16 + pos, 0, pos] = v
+    trits = oracle.unpack_packed_limbs(p, rows, K)
+    pd = cuda(p, dev)
+    for tok0 in range(0, 48, 16):
+        x = np.zeros((16, K), np.float32)
+        for i in range(16):
+            x[i, tok0 + i] = 1.0
+        for dt in (torch.bfloat16, torch.float32):
+            y = ops.gemm_trit(pd, cuda(x, dev, dt), M=rows, K=K, layout="nk", out_dtype=torch.float32)
+            assert np.array_equal(y.cpu().numpy().T, trits[:, tok0:tok0 + 16].astype(np.float32))
+
+
+# ---------------------------------------------------------------- TRIT mode, decode shapes
+
+
+def _linear_case(rng, out_f, in_f, tokens, rule="absmean"):
+    w = rng.normal(0, 0.02, (out_f, in_f)).astype(np.float32)
+    if rule == "absmean":
+        packed, scale = oracle.pack_dense_matrix_absmean(w, 0.45)
+    else:
+        packed, scale = oracle.pack_dense_matrix(w * 30, 0.45), None
+    x = rng.normal(size=(tokens, in_f)).astype(np.float32)
+    bias = rng.normal(0, 0.01, out_f).astype(np.float32)
+    return packed, scale, x, bias
+
+
+@pytest.mark.parametrize("out_f,in_f", [(16, 48), (100, 130), (256, 3072), (130, 4096), (384, 8192), (64, 14336),
+                                        (1000, 1000)])
+@pytest.mark.parametrize("tokens", [1, 4, 8, 9, 16])
+def test_gemv_bf16_matches_oracle(dev, out_f, in_f, tokens):
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(out_f * 7 + in_f * 3 + tokens)
+    packed, scale, x, bias = _linear_case(rng, out_f, in_f, tokens)
+    xb = cuda(x, dev, torch.bfloat16)
+    want = oracle.linear_forward(packed, scale, bias, xb.float().cpu().numpy(), in_f)
+    y32 = ops.gemm_trit(cuda(packed, dev), xb, M=out_f, K=in_f, layout="nk", row_scale=cuda(scale, dev),
+                        bias=cuda(bias, dev), out_dtype=torch.float32)
+    # fp32 accumulation of exact products: only the summation order differs from the oracle
+    assert rel_err(y32.cpu().numpy(), want) < 2e-5
+    y16 = ops.gemm_trit(cuda(packed, dev), xb, M=out_f, K=in_f, layout="nk", row_scale=cuda(scale, dev),
+                        bias=cuda(bias, dev))
+    assert y16.dtype == torch.bfloat16
+    assert rel_err(y16.float().cpu().numpy(), want) < 1e-2  # bf16 activations: 1e-2
+
+
+@pytest.mark.parametrize("tokens", [1, 5, 16])
+def test_gemv_fp32_activations_match_oracle(dev, tokens):
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(tokens)
+    packed, scale, x, bias = _linear_case(rng, 200, 1000, tokens, rule="fixed")
+    want = oracle.linear_forward(packed, None, bias, x, 1000)
+    y = ops.gemm_trit(cuda(packed, dev), cuda(x, dev), M=200, K=1000, layout="nk", bias=cuda(bias, dev))
+    assert y.dtype == torch.float32
+    assert rel_err(y.cpu().numpy(), want) < 1e-3  # fp32 activations: 1e-3 (achieved: ~1e-5)
+    assert rel_err(y.cpu().numpy(), want) < 5e-5
+    yh = ops.gemm_trit(cuda(packed, dev), cuda(x, dev, torch.float16), M=200, K=1000, layout="nk")
+    want_h = oracle.linear_forward(packed, None, None, cuda(x, dev, torch.float16).float().cpu().numpy(), 1000)
+    assert rel_err(yh.float().cpu().numpy(), want_h) < 2e-3
+
+
+def test_gemv_alpha_beta_and_strided_output(dev):
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(21)
+    packed, scale, x, bias = _linear_case(rng, 96, 500, 3)
+    xb = cuda(x, dev, torch.bfloat16)
+    c0 = rng.normal(size=(3, 96)).astype(np.float32)
+    C = cuda(c0, dev)
+    ops.gemm_trit(cuda(packed, dev), xb, M=96, K=500, layout="nk", C=C, alpha=0.5, beta=2.0)
+    base = oracle.linear_forward(packed, None, None, xb.float().cpu().numpy(), 500)
+    assert rel_err(C.cpu().numpy(), 0.5 * base + 2.0 * c0) < 2e-5
+    # output written into a column slice of a wider buffer (the sharded-Linear case)
+    wide = torch.zeros(3, 300, device=dev)
+    ops.gemm_trit(cuda(packed, dev), xb, M=96, K=500, layout="nk", C=wide[:, 100:196])
+    assert rel_err(wide[:, 100:196].cpu().numpy(), base) < 2e-5
+    assert not wide[:, :100].any() and not wide[:, 196:].any()
+
+
+def test_trit_ignores_trits_beyond_k(dev):
+    """K need not be a multiple of 48 and positions >= K never contribute, whatever the limb holds."""
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(22)
+    t = rng.integers(-1, 2, (40, 96)).astype(np.int8)
+    packed = oracle.pack_trits_rowwise(t)  # trits 70..95 are non-zero garbage for K = 70
+    x = rng.normal(size=(2, 70)).astype(np.float32)
+    want = x.astype(np.float64) @ t[:, :70].astype(np.float64).T
+    y = ops.gemm_trit(cuda(packed, dev), cuda(x, dev), M=40, K=70, layout="nk")
+    assert rel_err(y.cpu().numpy(), want) < 5e-5
+
+
+# ---------------------------------------------------------------- TRIT mode, general shapes (config 1 and friends)
+
+
+def test_config1_gemm_ternary_trit_mode(dev):
+    """BASELINE config 1: A 512x512 uniform trits packed by the reference packer rule,
+    B 512x256 fp32 N(0,1), C N(0,1), alpha 1, beta 0.5, fp32 accumulate."""
+    from t81lib_b200 import t81lib
+    rng = np.random.default_rng(1)
+    M, N, K = 512, 256, 512
+    trits = rng.integers(-1, 2, (M, K)).astype(np.int8)
+    A = oracle.pack_dense_matrix(trits.astype(np.float32), 0.5)  # (512, 11, 16), K padded to 528
+    B = rng.normal(size=(K, N)).astype(np.float32)
+    C0 = rng.normal(size=(M, N)).astype(np.float32)
+    Bp = np.zeros((528, N), np.float32); Bp[:K] = B
+    want = oracle.gemm_trit(A, Bp, C0, M, N, 528, 1.0, 0.5)
+    C = C0.copy()
+    t81lib.gemm_ternary(A.reshape(-1, 16).view("V16").reshape(M, 11), Bp, C, M, N, 528, alpha=1.0, beta=0.5)
+    assert rel_err(C, want) < 1e-3  # north-star tolerance for fp32
+    assert rel_err(C, want) < 5e-5  # what exact products with fp32 accumulation achieve
+    # on-device tensors, in place
+    Cd = cuda(C0, dev)
+    t81lib.gemm_ternary(cuda(A, dev), cuda(Bp, dev), Cd, M, N, 528, alpha=1.0, beta=0.5)
+    assert rel_err(Cd.cpu().numpy(), want) < 5e-5
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_general_kernel_layouts_and_dtypes(dev, layout, dtype, golden):
+    from t81lib_b200 import ops
+    g = golden("gemm_trit.npz")
+    x = cuda(g["x"], dev, dtype)  # (130, 11)
+    xr = x.float().cpu().numpy().astype(np.float64)
+    want = g["trits"].astype(np.float64) @ xr
+    if layout == "kn":
+        y = ops.gemm_trit(cuda(g["packed"], dev), x, M=24, K=130, layout="kn", out_dtype=torch.float32)
+        got = y.cpu().numpy()
+    else:
+        xt = x.t().contiguous()
+        big = torch.cat([xt, xt, xt])  # 33 tokens: beyond the streaming kernel's 16
+        y = ops.gemm_trit(cuda(g["packed"], dev), big, M=24, K=130, layout="nk", out_dtype=torch.float32)
+        got = y.cpu().numpy()[:11].T
+        assert torch.equal(y[:11], y[11:22]) and torch.equal(y[:11], y[22:])
+    assert rel_err(got, want) < 5e-5
+
+
+# ---------------------------------------------------------------- LIMB mode
+
+
+def test_limb_gemm_matches_reference_fixtures(dev, golden):
+    from t81lib_b200 import t81lib
+    g = golden("gemm_limb.npz")
+    for tag in ("nz10", "nz30", "nz48"):
+        A, B, C0, want = g[f"A_{tag}"], g[f"B_{tag}"], g[f"C0_{tag}"], g[f"C_{tag}"]
+        C = C0.copy()
+        t81lib.gemm_ternary(A.reshape(-1, 16).view("V16").reshape(9, 3), B.reshape(-1, 16).view("V16").reshape(3, 7),
+                            C, 9, 7, 144, alpha=1.25, beta=0.5)
+        np.testing.assert_allclose(C, want, rtol=1e-6)  # fp64 accumulation on both sides
+        Cd = cuda(C0, dev)
+        t81lib.gemm_ternary(cuda(A, dev), cuda(B, dev), Cd, 9, 7, 144, alpha=1.25, beta=0.5)
+        np.testing.assert_allclose(Cd.cpu().numpy(), want, rtol=1e-6)
+
+
+def test_limb_gemm_reference_known_answers(dev):
+    """tests/python/test_bindings.py:17-39 of the reference."""
+    import array
+    from t81lib_b200 import t81lib
+    M, N, K = 2, 3, 48
+    limb_pattern = bytes([13] * 16)
+    a_view = memoryview(bytearray(limb_pattern * (M * 1)))
+    b_view = memoryview(bytearray(limb_pattern * (1 * N)))
+    c_values = array.array("f", [0.0] * (M * N))
+    t81lib.gemm_ternary(a_view, b_view, c_values, M, N, K)
+    assert all(abs(v) <= 1e-6 for v in c_values)
+    c_values = array.array("f", [2.0] * (M * N))
+    t81lib.gemm_ternary(a_view, b_view, c_values, M, N, K, alpha=0.0, beta=0.5)
+    assert all(abs(v - 1.0) <= 1e-6 for v in c_values)
+
+
+def test_limb_gemm_matches_oracle_on_config1_shape(dev):
+    """Config 1's LIMB-mode run: B thresholded at 0.5 and column-packed, operands limited
+    to 10 non-zero trits per limb so the products stay finite in fp32."""
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(101)
+    M, N, KL = 512, 256, 11
+    ta = np.zeros((M, KL * 48), np.int8); tb = np.zeros((KL * 48, N), np.int8)
+    for l in range(KL):
+        ta[:, l * 48:l * 48 + 10] = rng.integers(-1, 2, (M, 10))
+        tb[l * 48:l * 48 + 10] = rng.integers(-1, 2, (10, N))
+    A, B = oracle.pack_trits_rowwise(ta), oracle.pack_trits_columnwise(tb)
+    C0 = rng.normal(size=(M, N)).astype(np.float32)
+    oracle.set_num_threads(8)
+    want = oracle.gemm_limb(A, B, C0, M, N, KL * 48, 1.0, 0.5)
+    oracle.set_num_threads(1)
+    Cd = cuda(C0, dev)
+    ops.gemm_limb(cuda(A, dev), cuda(B, dev), Cd, M, N, KL * 48, 1.0, 0.5)
+    np.testing.assert_allclose(Cd.cpu().numpy(), want, rtol=1e-6)
+
+
+# ---------------------------------------------------------------- Python surface
+
+
+def test_ternary_tensor_surface(dev):
+    """tests/python/test_torch_ternary.py:17-42 of the reference, plus values."""
+    import t81lib_b200.torch as t81_torch
+    weight = torch.linspace(-1.0, 1.0, steps=48, dtype=torch.float32).reshape(3, 16)
+    ternary = t81_torch.TernaryTensor.from_float(weight, threshold=0.45)  # CPU input is moved to the GPU
+    assert ternary.dtype is t81_torch.trit and tuple(ternary.shape) == (3, 16)
+    assert repr(ternary) == "TernaryTensor(shape=(3, 16), trits_per_row=16)"
+    assert np.array_equal(ternary.packed.cpu().numpy(), oracle.pack_dense_matrix(weight.numpy(), 0.45))
+    rhs = torch.randn(16, 4, dtype=torch.float32)
+    out = torch.matmul(ternary, rhs)
+    assert out.shape == (3, 4) and out.device.type == "cpu"  # result returns to the input's device
+    trits = oracle.quantize_to_trits(weight.numpy(), 0.45).astype(np.float32)
+    assert rel_err(out.numpy(), trits @ rhs.numpy()) < 1e-5
+    out = torch.mm(ternary, rhs.to(dev))
+    assert out.device == dev
+    y = ternary.matmul_input(rhs.t().contiguous().to(dev))
+    assert y.shape == (4, 3) and rel_err(y.cpu().numpy(), (trits @ rhs.numpy()).T) < 1e-5
+    with pytest.raises(ValueError, match="only support 2D"):
+        t81_torch.TernaryTensor.from_float(torch.zeros(2, 2, 2))
+    with pytest.raises(ValueError, match="expect 2D activations"):
+        ternary.matmul_input(torch.zeros(2, 2, 16, device=dev))
+    with pytest.raises(ValueError, match="does not match ternary weight width"):
+        ternary.matmul_input(torch.zeros(2, 17, device=dev))
+    with pytest.raises(NotImplementedError):
+        t81_torch.TernaryTensor.from_float(torch.zeros(2, 2, device="meta"))
+    # update_from_float re-packs in place
+    before = ternary.packed.data_ptr()
+    ternary.update_from_float(-weight)
+    assert ternary.packed.data_ptr() == before
+    assert np.array_equal(ternary.packed.cpu().numpy(), oracle.pack_dense_matrix(-weight.numpy(), 0.45))
+
+
+def test_matmul_input_backward_is_dense_transpose(dev):
+    import t81lib_b200.torch as t81_torch
+    rng = np.random.default_rng(8)
+    w = torch.from_numpy(rng.normal(0, 0.5, (12, 60)).astype(np.float32))
+    tern = t81_torch.TernaryTensor.from_float(w, threshold=0.45)
+    x = torch.randn(5, 60, device=dev, requires_grad=True)
+    bias = torch.randn(12, device=dev, requires_grad=True)
+    y = tern.matmul_input(x, bias=bias)
+    y.backward(torch.ones_like(y))
+    trits = torch.from_numpy(oracle.quantize_to_trits(w.numpy(), 0.45).astype(np.float32)).to(dev)
+    assert torch.allclose(x.grad, torch.ones(5, 12, device=dev) @ trits, atol=1e-5)
+    assert torch.allclose(bias.grad, torch.full((12,), 5.0, device=dev))
+
+
+def test_linear_eval_forward(dev):
+    from t81lib_b200.nn import Linear
+    torch.manual_seed(0)
+    for rule in ("fixed", "absmean"):
+        layer = Linear(300, 70, bias=True, threshold=0.45, rule=rule).to(dev).eval()
+        with torch.no_grad():
+            layer.weight.mul_(10.0 if rule == "fixed" else 1.0)
+        x = torch.randn(2, 5, 300, device=dev)
+        y = layer(x)
+        assert y.shape == (2, 5, 70)
+        w = layer.weight.detach().cpu().numpy()
+        if rule == "fixed":
+            packed, scale = oracle.pack_dense_matrix(w, 0.45), None
+        else:
+            packed, scale = oracle.pack_dense_matrix_absmean(w, 0.45)
+        want = oracle.linear_forward(packed, scale, layer.bias.detach().cpu().numpy(), x.reshape(10, 300).cpu().numpy(), 300)
+        assert rel_err(y.reshape(10, 70).cpu().numpy(), want) < 5e-5
+        assert layer.ternary_weight is not None
+        layer.train()
+        assert layer.ternary_weight is None  # cache dropped, as in the reference
+        layer.eval()
+        yb = layer(x.to(torch.bfloat16))
+        assert yb.dtype == torch.bfloat16
+        want_b = oracle.linear_forward(packed, scale, layer.bias.detach().cpu().numpy(),
+                                       x.to(torch.bfloat16).float().reshape(10, 300).cpu().numpy(), 300)
+        assert rel_err(yb.float().reshape(10, 70).cpu().numpy(), want_b) < 1e-2
+    with pytest.raises(ValueError, match="expects 2D or 3D inputs"):
+        layer(torch.zeros(1, 2, 3, 300, device=dev))
+
+
+def test_module_to_trit_patches_stock_linear(dev):
+    import t81lib_b200.torch as t81_torch
+    torch.manual_seed(1)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8)).to(dev)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(4.0)
+    model = model.to(dtype=t81_torch.trit)
+    x = torch.randn(6, 64, device=dev)
+    y = model(x)
+    w0 = oracle.quantize_to_trits(model[0].weight.detach().cpu().numpy(), 0.5).astype(np.float32)
+    w1 = oracle.quantize_to_trits(model[2].weight.detach().cpu().numpy(), 0.5).astype(np.float32)
+    h = np.maximum(x.cpu().numpy() @ w0.T + model[0].bias.detach().cpu().numpy(), 0)
+    want = h @ w1.T + model[2].bias.detach().cpu().numpy()
+    assert rel_err(y.detach().cpu().numpy(), want) < 5e-5
+    # an in-place weight update is picked up by the next forward (version counter)
+    with torch.no_grad():
+        model[2].weight.zero_()
+    y2 = model(x)
+    assert torch.allclose(y2, model[2].bias.expand_as(y2))
