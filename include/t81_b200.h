@@ -145,6 +145,15 @@ T81B200_API int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, cons
                       int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta,
                       void *workspace, size_t workspace_bytes, void *stream);
 
+/* Status word of the tensor-core kernel on the current device: 0 = no problem seen;
+ * 1..4 = a bounded wait inside the kernel expired (producer, MMA issuer, epilogue,
+ * converter) and that launch's output is invalid.  The kernel never spins forever:
+ * every wait has an iteration limit after which it records the code, releases its
+ * tensor memory and returns.  Reading the word synchronises the device; `reset`
+ * non-zero clears it.  No counterpart in the reference (its CUDA path has no
+ * asynchronous pipeline). */
+T81B200_API int t81b200_kernel_status(int reset);
+
 T81B200_API size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int c_dtype, int64_t M,
                                          int64_t N, int64_t K);
 

@@ -20,7 +20,7 @@ LAYOUT_KN, LAYOUT_NK = 0, 1
 EXPORTS = (
     "t81b200_device_available", "t81b200_last_error", "t81b200_version", "t81b200_quantize_pack",
     "t81b200_quantize_trits", "t81b200_unpack", "t81b200_gemm_limb", "t81b200_gemm_limb_host",
-    "t81b200_gemm_trit", "t81b200_gemm_trit_workspace_bytes",
+    "t81b200_gemm_trit", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
 )
 
 
@@ -33,10 +33,15 @@ class T81B200Error(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
-    if not os.path.exists(LIB_PATH):
-        raise ImportError(
-            f"{LIB_PATH} not found: build it with `python -m t81lib_b200.build` "
-            "(there is no fallback implementation)")
+    from . import build as _build
+    if _build._stale():
+        # sources changed since the library was built (or it was never built): rebuild in-tree
+        try:
+            _build.build()
+        except Exception as exc:  # no nvcc, compile error: there is nothing to fall back to
+            raise ImportError(
+                f"{LIB_PATH} is missing or out of date and could not be built: {exc} "
+                "(there is no fallback implementation)") from exc
     lib = ctypes.CDLL(LIB_PATH)
     i64, f32, vp, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int
     lib.t81b200_device_available.restype = ci
@@ -51,6 +56,7 @@ def _load() -> ctypes.CDLL:
                                       vp, ctypes.c_size_t, vp]
     lib.t81b200_gemm_trit_workspace_bytes.argtypes = [ci, ci, ci, i64, i64, i64]
     lib.t81b200_gemm_trit_workspace_bytes.restype = ctypes.c_size_t
+    lib.t81b200_kernel_status.argtypes = [ci]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is ctypes.c_int and name not in ("t81b200_device_available",):
@@ -79,6 +85,11 @@ def check(code: int) -> None:
 
 def device_available() -> bool:
     return bool(lib.t81b200_device_available())
+
+
+def kernel_status(reset: bool = False) -> int:
+    """Status word of the tensor-core kernel (0 = fine); synchronises the device."""
+    return lib.t81b200_kernel_status(1 if reset else 0)
 
 
 def version() -> str:

@@ -33,13 +33,28 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; libt81_b200.so cannot be built")
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
-        return True
-    built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(_CSRC, f) for f in os.listdir(_CSRC)]
+_STAMP = os.path.join(_LIBDIR, "BUILD_HASH")
+
+
+def source_hash() -> str:
+    """Hash of every source the library is built from (file times do not survive copies)."""
+    import hashlib
+    h = hashlib.sha256()
+    deps = sorted(os.path.join(_CSRC, f) for f in os.listdir(_CSRC))
     deps.append(os.path.join(os.path.dirname(_PKG), "include", "t81_b200.h"))
-    return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _stale() -> bool:
+    if not os.path.exists(LIB_PATH) or not os.path.exists(_STAMP):
+        return True
+    with open(_STAMP) as fh:
+        return fh.read().strip() != source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -69,6 +84,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}")
+    with open(_STAMP, "w") as fh:
+        fh.write(source_hash())
     return LIB_PATH
 
 

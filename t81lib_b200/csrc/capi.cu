@@ -80,9 +80,16 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
                         int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes,
                         cudaStream_t st);
 
+int gemm_trit_tc_status(int reset);
+
 }  // namespace t81b200
 
 using namespace t81b200;
+
+extern "C" int t81b200_kernel_status(int reset) {
+    if (int rc = check_device()) return rc;
+    return gemm_trit_tc_status(reset);
+}
 
 extern "C" const char *t81b200_last_error(void) { return g_error; }
 
@@ -124,8 +131,9 @@ extern "C" int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const
         const size_t need = gemm_trit_tc_workspace(b_dtype, layout, c_dtype, M, N, K);
         if (need > 0 && (!workspace || workspace_bytes < need))
             return fail(T81B200_EWORKSPACE, "gemm_trit: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
-        return gemm_trit_tc_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha,
-                                   beta, workspace, workspace_bytes, st);
+        const int rc = gemm_trit_tc_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K,
+                                           alpha, beta, workspace, workspace_bytes, st);
+        if (rc != T81B200_EALIGN) return rc;  // unaligned activations: the general kernel takes them
     }
     return gemm_trit_simt_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, st);
 }

@@ -1,15 +1,462 @@
-// Prefill-shaped TRIT-mode kernel on the 5th-generation tensor cores (placeholder
-// until the tcgen05 pipeline lands: reports "not eligible" so the dispatcher uses
-// the general kernel).
+// Prefill-shaped TRIT-mode kernel on the 5th-generation tensor cores (tcgen05).
+//
+//   D[o][t] = sum_k T[o][k] * x[t][k]       o: output feature (UMMA M = 128 per CTA tile)
+//                                            t: token          (UMMA N = 256 per CTA tile)
+// Operand A is produced on the fly: the packed limbs of 128 weight rows arrive by TMA as
+// raw bytes, converter warps expand them to exact bf16 {-1,0,+1} (packed bf16 FMAs, see
+// common.cuh) and write them in the K-major, 128-byte-swizzled layout UMMA expects.
+// Operand B is the activations, brought by TMA (SWIZZLE_128B) straight from (tokens, K)
+// bf16 memory.  Accumulators live in TMEM (2 x 256 fp32 columns, double-buffered across
+// tiles) and are read back with tcgen05.ld for a fused scale/bias/beta epilogue.
+//
+// One persistent CTA per SM, 14 warps:
+//   warp 0      TMA producer (raw weight bytes + activation tiles)
+//   warp 1      MMA issuer (one elected lane), owns the TMEM allocation
+//   warps 2-5   epilogue (TMEM lanes 32*(warp%4) ...)
+//   warps 6-13  converters (256 threads; 2 limbs per thread per 192-trit super-block)
+// The contraction runs in k-atoms of 64 (one 128-byte swizzle row); 48-trit limbs do not
+// divide 64, so converters work in super-blocks of 4 limbs = 192 trits = 3 atoms.
+//
+// Every mbarrier wait is bounded; on expiry the role records a status code and all roles
+// fall through to the common teardown (TMEM is always released).
 #include "common.cuh"
+
+#include <cuda.h>
 
 namespace t81b200 {
 
-bool gemm_trit_tc_eligible(int, int, int, int64_t, int64_t, int64_t) { return false; }
+namespace {
+
+constexpr int BM = 128;          // output features per tile (UMMA M)
+constexpr int BN = 256;          // tokens per tile (UMMA N)
+constexpr int BK = 64;           // k-atom: 64 bf16 = 128 bytes
+constexpr int A_STAGES = 6;      // two super-blocks of expanded weights
+constexpr int B_STAGES = 3;
+constexpr int RAW_STAGES = 2;
+constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;    // 32 KB
+constexpr int RAW_STAGE_BYTES = BM * 64;      // 4 limbs per row: 8 KB
+constexpr int NUM_THREADS = 14 * 32;
+constexpr int CONVERTER_WARP0 = 6;
+constexpr int CONVERTER_WARPS = 8;
+constexpr int SMEM_DATA_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + RAW_STAGES * RAW_STAGE_BYTES;
+constexpr int SMEM_BYTES = SMEM_DATA_BYTES + 256 /*barriers*/ + 1024 /*alignment slack*/;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+enum { STATUS_OK = 0, STATUS_TIMEOUT_PRODUCER = 1, STATUS_TIMEOUT_MMA = 2, STATUS_TIMEOUT_EPILOGUE = 3, STATUS_TIMEOUT_CONVERTER = 4 };
+
+__device__ int g_tc_status = 0;
+
+struct TcParams {
+    const float *row_scale, *bias;
+    void *C;
+    int64_t ldc, M, N, K, kl;
+    int m_tiles, n_tiles, n_atoms;
+    float alpha, beta;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (spin > 1024) __nanosleep(64);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// K-major, SWIZZLE_128B shared-memory descriptor: rows are 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);  // start address
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+    d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct Ring {
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int stages) {
+        if (++stage == stages) { stage = 0; phase ^= 1; }
+    }
+};
+
+template <typename CT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_smem = base;
+    const uint32_t b_smem = a_smem + A_STAGES * A_STAGE_BYTES;
+    const uint32_t raw_smem = b_smem + B_STAGES * B_STAGE_BYTES;
+    const uint32_t bars = raw_smem + RAW_STAGES * RAW_STAGE_BYTES;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    // barrier slots (8 bytes each)
+    auto a_full = [&](int s) { return bars + 8u * s; };
+    auto a_empty = [&](int s) { return bars + 8u * (A_STAGES + s); };
+    auto b_full = [&](int s) { return bars + 8u * (2 * A_STAGES + s); };
+    auto b_empty = [&](int s) { return bars + 8u * (2 * A_STAGES + B_STAGES + s); };
+    auto raw_full = [&](int s) { return bars + 8u * (2 * A_STAGES + 2 * B_STAGES + s); };
+    auto raw_empty = [&](int s) { return bars + 8u * (2 * A_STAGES + 2 * B_STAGES + RAW_STAGES + s); };
+    auto acc_full = [&](int s) { return bars + 8u * (2 * A_STAGES + 2 * B_STAGES + 2 * RAW_STAGES + s); };
+    auto acc_empty = [&](int s) { return bars + 8u * (2 * A_STAGES + 2 * B_STAGES + 2 * RAW_STAGES + 2 + s); };
+    const uint32_t tmem_slot = bars + 8u * (2 * A_STAGES + 2 * B_STAGES + 2 * RAW_STAGES + 4);
+    volatile uint32_t *tmem_slot_gen = reinterpret_cast<volatile uint32_t *>(
+        gen_base + SMEM_DATA_BYTES + 8 * (2 * A_STAGES + 2 * B_STAGES + 2 * RAW_STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < A_STAGES; ++s) { mbar_init(a_full(s), CONVERTER_WARPS); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+        for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), CONVERTER_WARPS); }
+        for (int s = 0; s < 2; ++s) { mbar_init(acc_full(s), 1); mbar_init(acc_empty(s), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int n_super = (p.n_atoms + 2) / 3;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            Ring raw, b;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+                for (int s = 0; s < n_super && ok; ++s) {
+                    ok = mbar_wait(raw_empty(raw.stage), raw.phase ^ 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(raw_full(raw.stage), RAW_STAGE_BYTES);
+                    tma_load_2d(raw_smem + raw.stage * RAW_STAGE_BYTES, &map_w, s * 64, m0, raw_full(raw.stage));
+                    raw.advance(RAW_STAGES);
+                    for (int a = 3 * s; a < 3 * s + 3 && a < p.n_atoms; ++a) {
+                        ok = mbar_wait(b_empty(b.stage), b.phase ^ 1);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(b_full(b.stage), B_STAGE_BYTES);
+                        tma_load_2d(b_smem + b.stage * B_STAGE_BYTES, &map_x, a * BK, n0, b_full(b.stage));
+                        b.advance(B_STAGES);
+                    }
+                }
+            }
+            if (!ok) atomicCAS(&g_tc_status, STATUS_OK, STATUS_TIMEOUT_PRODUCER);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            Ring a, b;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                ok = mbar_wait(acc_empty(buf), acc_phase ^ 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                for (int at = 0; at < p.n_atoms; ++at) {
+                    ok = mbar_wait(a_full(a.stage), a.phase) && mbar_wait(b_full(b.stage), b.phase);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t ad = umma_desc(a_smem + a.stage * A_STAGE_BYTES);
+                    const uint64_t bd = umma_desc(b_smem + b.stage * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), (at | k) != 0 ? 1u : 0u);
+                    umma_commit(a_empty(a.stage));
+                    umma_commit(b_empty(b.stage));
+                    a.advance(A_STAGES);
+                    b.advance(B_STAGES);
+                }
+                if (!ok) break;
+                umma_commit(acc_full(buf));
+            }
+            if (!ok) atomicCAS(&g_tc_status, STATUS_OK, STATUS_TIMEOUT_MMA);
+        }
+    } else if (warp < CONVERTER_WARP0) {
+        // ---------------- epilogue ----------------
+        const int lane_group = warp & 3;  // TMEM lanes 32*lane_group .. +31 are this warp's
+        bool ok = true;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
+            const int buf = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), acc_phase));  // warp-uniform: tcgen05.ld is .aligned
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t row = (int64_t)m0 + lane_group * 32 + lane;
+            const bool row_ok = row < p.M;
+            const float scale = (row_ok && p.row_scale ? p.row_scale[row] : 1.0f) * p.alpha;
+            const float bias = row_ok && p.bias ? p.bias[row] : 0.0f;
+            CT *crow = static_cast<CT *>(p.C) + row;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + c * 32), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int64_t tok = (int64_t)n0 + c * 32 + i;
+                        if (tok < p.N) {
+                            float y = __uint_as_float(v[i]) * scale + bias;
+                            CT *dst = crow + tok * p.ldc;
+                            if (p.beta != 0.0f) y += p.beta * to_float<CT>(*dst);
+                            *dst = from_float<CT>(y);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
+        if (!ok && lane == 0) atomicCAS(&g_tc_status, STATUS_OK, STATUS_TIMEOUT_EPILOGUE);
+    } else {
+        // ---------------- converters ----------------
+        const int cthread = threadIdx.x - CONVERTER_WARP0 * 32;  // 0..255
+        Ring raw, a;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int s = 0; s < n_super && ok; ++s) {
+                ok = __all_sync(0xffffffffu, mbar_wait(raw_full(raw.stage), raw.phase));
+                if (!ok) break;
+                uint4 limb[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int item = cthread + 256 * h;  // row = item / 4, limb = item % 4
+                    limb[h] = *reinterpret_cast<const uint4 *>(gen_base + A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES +
+                                                               raw.stage * RAW_STAGE_BYTES + item * 16);
+                    if ((int64_t)4 * s + (item & 3) >= p.kl)  // past the row's last limb: zero trits
+                        limb[h] = make_uint4(kZeroTryteWord, kZeroTryteWord, kZeroTryteWord, kZeroTryteWord);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(raw_empty(raw.stage));
+                raw.advance(RAW_STAGES);
+
+                // the (up to) three atoms of this super-block
+                const int atoms_here = p.n_atoms - 3 * s < 3 ? p.n_atoms - 3 * s : 3;
+                Ring aw = a;
+                for (int j = 0; j < atoms_here && ok; ++j) {
+                    ok = mbar_wait(a_empty(aw.stage), aw.phase ^ 1);
+                    aw.advance(A_STAGES);
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int item = cthread + 256 * h;
+                    const int r = item >> 2, j = item & 3;
+                    uint32_t o[24];
+                    decode_limb(limb[h], o);
+                    // decode order -> natural order: pairs (trit 2m, trit 2m+1)
+                    uint32_t nat[24];
+#pragma unroll
+                    for (int pr = 0; pr < 8; ++pr) {
+                        nat[3 * pr + 0] = __byte_perm(o[3 * pr], o[3 * pr + 1], 0x5410);
+                        nat[3 * pr + 1] = __byte_perm(o[3 * pr + 2], o[3 * pr], 0x7610);
+                        nat[3 * pr + 2] = __byte_perm(o[3 * pr + 1], o[3 * pr + 2], 0x7632);
+                    }
+                    const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+#pragma unroll
+                    for (int q = 0; q < 6; ++q) {
+                        const int chunk = 6 * j + q;         // 16-byte chunk inside the 384-byte super-block row
+                        const int atom = chunk >> 3, cc = chunk & 7;
+                        if (atom < atoms_here) {
+                            int st = a.stage + atom;
+                            st = st >= A_STAGES ? st - A_STAGES : st;
+                            const uint32_t off = (uint32_t)st * A_STAGE_BYTES + row_off + (uint32_t)((cc ^ (r & 7)) << 4);
+                            *reinterpret_cast<uint4 *>(gen_base + off) = make_uint4(nat[4 * q], nat[4 * q + 1], nat[4 * q + 2], nat[4 * q + 3]);
+                        }
+                    }
+                }
+                // generic-proxy writes must be visible to the tensor core's async proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0)
+                    for (int j = 0; j < atoms_here; ++j) {
+                        int st = a.stage + j;
+                        st = st >= A_STAGES ? st - A_STAGES : st;
+                        mbar_arrive(a_full(st));
+                    }
+                a = aw;
+            }
+        }
+        if (!ok && lane == 0) atomicCAS(&g_tc_status, STATUS_OK, STATUS_TIMEOUT_CONVERTER);
+    }
+
+    // ---------------- teardown ----------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host: tensor maps through the driver entry point (no link-time libcuda dependency) ----
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+int make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, size_t elem, const void *ptr, uint64_t inner, uint64_t outer,
+                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return fail(T81B200_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem;
+    CUresult rc = fn(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(T81B200_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return T81B200_OK;
+}
+
+template <typename CT>
+int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, cudaStream_t st) {
+    auto kern = gemm_trit_tc_kernel<CT>;
+    static bool configured = false;
+    if (!configured) {
+        T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(mw, mx, p);
+    T81_LAUNCH_CHECK("gemm_trit_tc_kernel");
+    return T81B200_OK;
+}
+
+}  // namespace
+
+// The tensor-core path takes bf16 activations in the token-major (NK) layout with 16-byte
+// aligned rows; everything else goes to the general kernel.
+bool gemm_trit_tc_eligible(int b_dtype, int layout, int c_dtype, int64_t M, int64_t N, int64_t K) {
+    (void)c_dtype;
+    return b_dtype == T81B200_BF16 && layout == T81B200_LAYOUT_NK && N > 16 && M >= 1 && K >= 1 &&
+           M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31);
+}
+
 size_t gemm_trit_tc_workspace(int, int, int, int64_t, int64_t, int64_t) { return 0; }
-int gemm_trit_tc_launch(const uint8_t *, const float *, const void *, int, int, int64_t, const float *, void *, int,
-                        int64_t, int64_t, int64_t, int64_t, float, float, void *, size_t, cudaStream_t) {
-    return fail(T81B200_EINVAL, "tensor-core kernel not built");
+
+int gemm_trit_tc_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof v) != cudaSuccess) return T81B200_ECUDA;
+    if (reset && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_tc_status, &zero, sizeof zero) != cudaSuccess) return T81B200_ECUDA;
+    }
+    return v;
+}
+
+int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
+                        int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int64_t N,
+                        int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    (void)workspace; (void)workspace_bytes; (void)b_dtype; (void)layout;
+    if (reinterpret_cast<uintptr_t>(B) % 16 != 0 || (ldb * 2) % 16 != 0)
+        return T81B200_EALIGN;  // caller falls back to the general kernel
+    const int64_t kl = (K + 47) / 48;
+    CUtensorMap mw, mx;
+    if (int rc = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)kl * 16, (uint64_t)M, (uint64_t)kl * 16, 64, BM,
+                             CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+    if (int rc = make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+        return rc;
+    TcParams p;
+    p.row_scale = row_scale; p.bias = bias; p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.kl = kl;
+    p.m_tiles = (int)((M + BM - 1) / BM);
+    p.n_tiles = (int)((N + BN - 1) / BN);
+    p.n_atoms = (int)((K + BK - 1) / BK);
+    p.alpha = alpha; p.beta = beta;
+    switch (c_dtype) {
+        case T81B200_F32: return launch_tc<float>(mw, mx, p, st);
+        case T81B200_BF16: return launch_tc<__nv_bfloat16>(mw, mx, p, st);
+        case T81B200_F16: return launch_tc<__half>(mw, mx, p, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
 }
 
 }  // namespace t81b200

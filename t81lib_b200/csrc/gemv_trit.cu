@@ -6,11 +6,13 @@
 // the expanded weights never touch shared or global memory.
 //
 // Work split
-//   grid.x : row tiles of 128*RG rows (8 warps, RG groups of 16 rows per warp)
-//   grid.y : S slices of the contraction, S = cluster size (1..8).  The S CTAs of
-//            a cluster hold partial sums for the same rows; they are combined
-//            through distributed shared memory in rank order (deterministic), so
-//            no global scratch and no atomics are involved.
+//   CTA    : W = 8 or 16 warps arranged as RW row groups (16 rows each) x W/RW slices of
+//            the contraction; the slices' partial sums meet in shared memory.
+//   grid.x : row tiles of 16*RW*RG rows (RG groups walked in sequence)
+//   grid.y : S more slices of the contraction, S = cluster size (1..8), for shapes with
+//            too few rows to fill the GPU.  The S CTAs of a cluster combine their partial
+//            sums through distributed shared memory in rank order (deterministic): no
+//            global scratch and no atomics are involved.
 //   lane (g = lane/4, t = lane%4) of a warp loads, for each chunk of 4 limbs,
 //   limb 4c+t of rows g and g+8.  The order of the contraction index inside an
 //   MMA is free as long as both operands agree, so the activations are staged in
@@ -19,14 +21,15 @@
 
 #include <cooperative_groups.h>
 
+#include <cmath>
+#include <cstdlib>
+
 namespace cg = cooperative_groups;
 
 namespace t81b200 {
 
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
 constexpr int kPrefetch = 4;  // chunks of 4 limbs in flight per lane
 
 struct GemvParams {
@@ -38,7 +41,8 @@ struct GemvParams {
     int64_t M, K, kl, ldx, ldc;
     int ntok;
     int limbs_per_slice;    // multiple of 4
-    int row_groups;         // RG
+    int row_groups;         // RG: 16-row groups each row-warp walks in sequence
+    int row_warps;          // RW: warps side by side along the rows; W/RW warps split the contraction
     float alpha, beta;
 };
 
@@ -67,12 +71,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Stage the activations of limbs [L0, L0+nl) for `ntok` tokens into shared memory in
 // decode_limb register order.  Plane 0 holds bf16(x); plane 1 (PLANES == 2) holds
 // bf16(x - plane0), so that plane0 + plane1 carries 16 mantissa bits of an fp32 input.
-template <typename XT, int PLANES>
+template <typename XT, int PLANES, int THREADS>
 __device__ __forceinline__ void stage_activations(const GemvParams &p, int L0, int nl, uint32_t *xs,
                                                   int tok_stride, int plane_stride) {
     const XT *X = static_cast<const XT *>(p.X);
     const bool vec_ok = sizeof(XT) == 2 && (reinterpret_cast<uintptr_t>(X) % 16 == 0) && (p.ldx % 8 == 0);
-    for (int item = threadIdx.x; item < p.ntok * nl; item += kThreads) {
+    for (int item = threadIdx.x; item < p.ntok * nl; item += THREADS) {
         const int tok = item / nl, l = item - tok * nl;
         const int64_t k0 = (int64_t)(L0 + l) * 48;
         uint32_t *dst = xs + tok * tok_stride + l * 24;
@@ -129,9 +133,11 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int64_t row, int 
 template <typename XT> struct Planes { static constexpr int value = 2; };
 template <> struct Planes<__nv_bfloat16> { static constexpr int value = 1; };
 
-template <typename XT, typename CT, int TOKB>
-__global__ void __launch_bounds__(kThreads, 2) gemv_trit_kernel(const GemvParams p) {
+template <typename XT, typename CT, int TOKB, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_trit_kernel(const GemvParams p) {
     constexpr int PLANES = Planes<XT>::value;
+    constexpr int THREADS = WARPS * 32;
+    constexpr int kTokPad = 8 * TOKB;
     extern __shared__ __align__(16) uint32_t smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int slices = (int)cluster.num_blocks();
@@ -139,70 +145,94 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_trit_kernel(const GemvParams
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int rw = warp % p.row_warps;   // which 16-row group of the tile
+    const int kw = warp / p.row_warps;   // which slice of the CTA's contraction range
+    const int k_warps = WARPS / p.row_warps;
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
     const int L0 = slice * p.limbs_per_slice;
     int nl = kl4 - L0;
     nl = nl < 0 ? 0 : (nl > p.limbs_per_slice ? p.limbs_per_slice : nl);
 
-    // shared memory: [activations: PLANES x ntok x tok_stride] [partials: rows x 8*TOKB floats]
+    // shared memory: [activations: PLANES x ntok x tok_stride] [partials: k_warps x rows x kTokPad floats]
     const int tok_stride = p.limbs_per_slice * 24 + 4;  // +16 bytes: conflict-free 128-bit reads
     const int plane_stride = p.ntok * tok_stride;
     uint32_t *xs = smem;
     float *part = reinterpret_cast<float *>(smem + PLANES * plane_stride);
-    constexpr int kTokPad = 8 * TOKB;
-    const int rows_per_cta = kWarps * 16 * p.row_groups;
-
-    stage_activations<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride);
-    __syncthreads();
-
+    const int rows_per_cta = p.row_warps * 16 * p.row_groups;
     const int64_t cta_row0 = (int64_t)blockIdx.x * rows_per_cta;
-    const int chunks = nl >> 2;
-    const uint4 zero_limb = make_uint4(kZeroTryteWord, kZeroTryteWord, kZeroTryteWord, kZeroTryteWord);
 
-    for (int rg = 0; rg < p.row_groups; ++rg) {
-        const int64_t r0 = cta_row0 + (int64_t)(rg * kWarps + warp) * 16;
-        if (r0 >= p.M) continue;  // nothing to add; the reduction never stores rows >= M
+    // chunk range (4 limbs per chunk) of this warp inside the CTA's range
+    const int chunks_cta = nl >> 2;
+    const int cpw = (chunks_cta + k_warps - 1) / k_warps;
+    const int c_begin = kw * cpw < chunks_cta ? kw * cpw : chunks_cta;
+    const int c_end = c_begin + cpw < chunks_cta ? c_begin + cpw : chunks_cta;
+    const int last_limb = (int)p.kl - 1;
+
+    // Row pointers of row group `rg` for this lane (clamped: rows >= M are never stored).
+    const uint4 *pa, *pb;
+    auto set_rows = [&](int rg) {
+        const int64_t r0 = cta_row0 + (int64_t)(rg * p.row_warps + rw) * 16;
         int64_t ra = r0 + g, rb = r0 + g + 8;
         ra = ra < p.M ? ra : p.M - 1;
         rb = rb < p.M ? rb : p.M - 1;
-        const uint4 *pa = reinterpret_cast<const uint4 *>(p.A) + ra * p.kl + L0 + t;
-        const uint4 *pb = reinterpret_cast<const uint4 *>(p.A) + rb * p.kl + L0 + t;
+        pa = reinterpret_cast<const uint4 *>(p.A) + ra * p.kl;
+        pb = reinterpret_cast<const uint4 *>(p.A) + rb * p.kl;
+    };
+    // Limb index of chunk c for this lane.  Past the row's last limb the last limb is read
+    // again: the activations staged for those positions are zero, so it contributes nothing.
+    auto limb_of = [&](int c) {
+        const int l = L0 + 4 * c + t;
+        return l < last_limb ? l : last_limb;
+    };
+    uint4 qa[kPrefetch], qb[kPrefetch];
+    auto prefetch_head = [&]() {
+#pragma unroll
+        for (int s = 0; s < kPrefetch; ++s) {
+            const int l = limb_of(c_begin + s < c_end ? c_begin + s : c_begin);
+            qa[s] = ldg_stream(pa + l);
+            qb[s] = ldg_stream(pb + l);
+        }
+    };
 
+    // The weight stream does not depend on shared memory: get its first loads in flight
+    // before the activations are staged.
+    set_rows(0);
+    if (c_begin < c_end) prefetch_head();
+    stage_activations<XT, PLANES, THREADS>(p, L0, nl, xs, tok_stride, plane_stride);
+    __syncthreads();
+
+    // lanes whose token does not exist read token 0; their results are never stored
+    int tok_off[TOKB];
+#pragma unroll
+    for (int b = 0; b < TOKB; ++b) tok_off[b] = (8 * b + g < p.ntok ? 8 * b + g : 0) * tok_stride + t * 24;
+
+    for (int rg = 0; rg < p.row_groups; ++rg) {
         float acc[TOKB][4];
 #pragma unroll
         for (int b = 0; b < TOKB; ++b) acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.0f;
 
-        uint4 qa[kPrefetch], qb[kPrefetch];
-#pragma unroll
-        for (int s = 0; s < kPrefetch; ++s) {
-            const bool in = s < chunks && (L0 + 4 * s + t) < p.kl;
-            qa[s] = in ? ldg_stream(pa + 4 * s) : zero_limb;
-            qb[s] = in ? ldg_stream(pb + 4 * s) : zero_limb;
-        }
-
-        for (int c0 = 0; c0 < chunks; c0 += kPrefetch) {
+        for (int c0 = c_begin; c0 < c_end; c0 += kPrefetch) {
 #pragma unroll
             for (int s = 0; s < kPrefetch; ++s) {
                 const int c = c0 + s;
-                if (c < chunks) {
+                if (c < c_end) {
                     uint32_t wa[24], wb[24];
                     decode_limb(qa[s], wa);
                     decode_limb(qb[s], wb);
                     const int cn = c + kPrefetch;
-                    const bool in = cn < chunks && (L0 + 4 * cn + t) < p.kl;
-                    qa[s] = in ? ldg_stream(pa + 4 * cn) : zero_limb;
-                    qb[s] = in ? ldg_stream(pb + 4 * cn) : zero_limb;
+                    if (cn < c_end) {
+                        const int l = limb_of(cn);
+                        qa[s] = ldg_stream(pa + l);
+                        qb[s] = ldg_stream(pb + l);
+                    }
 #pragma unroll
                     for (int b = 0; b < TOKB; ++b) {
-                        const int tok = 8 * b + g;
 #pragma unroll
                         for (int pl = 0; pl < PLANES; ++pl) {
-                            const uint4 *xv = reinterpret_cast<const uint4 *>(
-                                xs + pl * plane_stride + tok * tok_stride + (4 * c + t) * 24);
+                            const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96);
 #pragma unroll
                             for (int q = 0; q < 6; ++q) {
-                                uint4 x = make_uint4(0, 0, 0, 0);
-                                if (tok < p.ntok) x = xv[q];
+                                const uint4 x = xv[q];
                                 mma_bf16_16816(acc[b], wa[4 * q], wb[4 * q], wa[4 * q + 1], wb[4 * q + 1], x.x, x.y);
                                 mma_bf16_16816(acc[b], wa[4 * q + 2], wb[4 * q + 2], wa[4 * q + 3], wb[4 * q + 3], x.z, x.w);
                             }
@@ -212,34 +242,43 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_trit_kernel(const GemvParams
             }
         }
 
+        if (rg + 1 < p.row_groups) {  // next group's first loads overlap this group's stores
+            set_rows(rg + 1);
+            if (c_begin < c_end) prefetch_head();
+        }
+
         // acc[b][0]: (row g, token 8b+2t), [1]: (row g, 8b+2t+1), [2]: (row g+8, 8b+2t), [3]: (row g+8, 8b+2t+1)
-        if (slices == 1) {
+        const int lr = (rg * p.row_warps + rw) * 16;  // local row of this warp's group
+        float *pw = part + (size_t)kw * rows_per_cta * kTokPad;
 #pragma unroll
-            for (int b = 0; b < TOKB; ++b) {
-                store_out<CT>(p, r0 + g, 8 * b + 2 * t, acc[b][0]);
-                store_out<CT>(p, r0 + g, 8 * b + 2 * t + 1, acc[b][1]);
-                store_out<CT>(p, r0 + g + 8, 8 * b + 2 * t, acc[b][2]);
-                store_out<CT>(p, r0 + g + 8, 8 * b + 2 * t + 1, acc[b][3]);
-            }
-        } else {
-            const int lr = (rg * kWarps + warp) * 16;  // local row of this warp's group
-#pragma unroll
-            for (int b = 0; b < TOKB; ++b) {
-                float *d0 = part + (lr + g) * kTokPad + 8 * b + 2 * t;
-                float *d1 = part + (lr + g + 8) * kTokPad + 8 * b + 2 * t;
-                *reinterpret_cast<float2 *>(d0) = make_float2(acc[b][0], acc[b][1]);
-                *reinterpret_cast<float2 *>(d1) = make_float2(acc[b][2], acc[b][3]);
-            }
+        for (int b = 0; b < TOKB; ++b) {
+            *reinterpret_cast<float2 *>(pw + (lr + g) * kTokPad + 8 * b + 2 * t) = make_float2(acc[b][0], acc[b][1]);
+            *reinterpret_cast<float2 *>(pw + (lr + g + 8) * kTokPad + 8 * b + 2 * t) = make_float2(acc[b][2], acc[b][3]);
         }
     }
+    __syncthreads();
 
-    if (slices > 1) {
+    // Fold the k-warps' partials in a fixed order (deterministic), then, with more than one
+    // CTA per cluster, the ranks' partials through distributed shared memory.
+    const int outs = rows_per_cta * kTokPad;
+    if (slices == 1) {
+        for (int idx = threadIdx.x; idx < outs; idx += THREADS) {
+            float s = part[idx];
+            for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
+            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < outs; idx += THREADS) {
+            float s = part[idx];
+            for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
+            part[idx] = s;
+        }
         cluster.sync();
         // CTA `slice` finishes rows [slice*span, (slice+1)*span) of the tile, summing ranks 0..S-1 in order.
         const int span = (rows_per_cta + slices - 1) / slices;
         const int lo = slice * span;
         const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
-        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += kThreads) {
+        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += THREADS) {
             float s = 0.0f;
             for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
             store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
@@ -248,15 +287,15 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_trit_kernel(const GemvParams
     }
 }
 
-template <typename XT, typename CT, int TOKB>
+template <typename XT, typename CT, int TOKB, int WARPS>
 int launch(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) {
-    auto kern = gemv_trit_kernel<XT, CT, TOKB>;
+    auto kern = gemv_trit_kernel<XT, CT, TOKB, WARPS>;
     if (smem_bytes > 48 * 1024)
         T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    const int rows_per_cta = kWarps * 16 * p.row_groups;
+    const int rows_per_cta = p.row_warps * 16 * p.row_groups;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((p.M + rows_per_cta - 1) / rows_per_cta), (unsigned)slices, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -271,18 +310,24 @@ int launch(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) 
 }
 
 template <typename XT, typename CT>
-int launch_tokb(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) {
-    return p.ntok > 8 ? launch<XT, CT, 2>(p, slices, smem_bytes, st) : launch<XT, CT, 1>(p, slices, smem_bytes, st);
+int launch_tokb(const GemvParams &p, int warps, int slices, size_t smem_bytes, cudaStream_t st) {
+    if (p.ntok > 8)
+        return warps == 8 ? launch<XT, CT, 2, 8>(p, slices, smem_bytes, st) : launch<XT, CT, 2, 16>(p, slices, smem_bytes, st);
+    return warps == 8 ? launch<XT, CT, 1, 8>(p, slices, smem_bytes, st) : launch<XT, CT, 1, 16>(p, slices, smem_bytes, st);
 }
 
 template <typename XT>
-int launch_ct(const GemvParams &p, int c_dtype, int slices, size_t smem_bytes, cudaStream_t st) {
+int launch_ct(const GemvParams &p, int c_dtype, int warps, int slices, size_t smem_bytes, cudaStream_t st) {
     switch (c_dtype) {
-        case T81B200_F32: return launch_tokb<XT, float>(p, slices, smem_bytes, st);
-        case T81B200_BF16: return launch_tokb<XT, __nv_bfloat16>(p, slices, smem_bytes, st);
-        case T81B200_F16: return launch_tokb<XT, __half>(p, slices, smem_bytes, st);
+        case T81B200_F32: return launch_tokb<XT, float>(p, warps, slices, smem_bytes, st);
+        case T81B200_BF16: return launch_tokb<XT, __nv_bfloat16>(p, warps, slices, smem_bytes, st);
+        case T81B200_F16: return launch_tokb<XT, __half>(p, warps, slices, smem_bytes, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
+}
+
+size_t gemv_smem_bytes(int planes, int ntok, int tokpad, int lps, int warps, int row_warps, int rg) {
+    return (size_t)planes * ntok * (lps * 24 + 4) * 4 + (size_t)(warps / row_warps) * row_warps * 16 * rg * tokpad * 4;
 }
 
 }  // namespace
@@ -299,39 +344,62 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     const int tokpad = ntok > 8 ? 16 : 8;
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
 
-    // Choose rows per CTA and the number of K slices so that about three waves of CTAs
-    // exist and a slice's activations fit in shared memory next to a second CTA.
+    // Pick the CTA shape with a small cost model.  A CTA has W warps arranged as RW row groups
+    // (16 rows each) x W/RW slices of its contraction range; RG row groups are walked in
+    // sequence; S CTAs of a cluster split the contraction further.  One CTA per SM per wave:
+    //   time = waves * (fixed + staging + max(stream, issue))
     const int sms = sm_count();
-    const size_t smem_budget = 100 * 1024;
-    int best_rg = 1, best_s = 1;
-    double best_score = -1.0;
-    for (int rg = 1; rg <= 4; rg *= 2) {
-        const int rows_per_cta = kWarps * 16 * rg;
-        const int64_t row_tiles = (M + rows_per_cta - 1) / rows_per_cta;
-        for (int s = 1; s <= 8; s *= 2) {
-            int lps = (kl4 / 4 + s - 1) / s * 4;
+    const double sm_bw = 6.5e12 / sms;   // HBM share of one SM, bytes/s
+    const double l2_bw = 1.0e11;         // L2 -> one SM, bytes/s (staging of activations)
+    const double issue = 4 * 0.6 * 1.7e9;  // warp instructions per second one SM sustains here
+    int best_w = 16, best_rw = 4, best_rg = 1, best_s = 1, best_lps = 4;
+    double best_t = 1e30;
+    for (int w = 8; w <= 16; w += 8)
+        for (int rwv = 1; rwv <= w; rwv *= 2)
+            for (int rg = 1; rg <= 4; rg *= 2)
+                for (int s = 1; s <= 8; s *= 2) {
+                    const int rows_per_cta = rwv * 16 * rg;
+                    int lps = (kl4 / 4 + s - 1) / s * 4;
+                    if (lps < 4) lps = 4;
+                    if (s > 1 && (int64_t)(s - 1) * lps >= kl4) continue;  // an empty slice
+                    const int kwv = w / rwv;
+                    if (kwv > lps / 4) continue;                           // a warp without work
+                    const size_t smem = gemv_smem_bytes(planes, ntok, tokpad, lps, w, rwv, rg);
+                    if (smem > 200 * 1024) continue;
+                    const int64_t row_tiles = (M + rows_per_cta - 1) / rows_per_cta;
+                    const double ctas = (double)row_tiles * s;
+                    const double waves = ceil(ctas / sms);
+                    const double stream = (double)rows_per_cta * lps * 16 / sm_bw;
+                    const double chunks = (double)rwv * rg * (lps / 4.0);
+                    const double work = chunks * (150.0 + 60.0 * planes * (tokpad / 8)) / issue;
+                    const double staging = (double)planes * ntok * lps * 96 / l2_bw;
+                    const double fixed = 1.0e-6 + (s > 1 ? 1.5e-6 : 0.0);
+                    const double t = waves * (fixed + staging + (stream > work ? stream : work));
+                    if (t < best_t) { best_t = t; best_w = w; best_rw = rwv; best_rg = rg; best_s = s; best_lps = lps; }
+                }
+    if (best_t >= 1e30)
+        return fail(T81B200_ELIMIT, "gemm_trit: K=%lld too large for the streaming kernel", (long long)K);
+    // Tuning override: T81B200_GEMV_CFG="warps,row_warps,row_groups,slices" (used by sweeps; unset in production).
+    if (const char *env = getenv("T81B200_GEMV_CFG")) {
+        int w = 0, rwv = 0, rg = 0, sl = 0;
+        if (sscanf(env, "%d,%d,%d,%d", &w, &rwv, &rg, &sl) == 4 && (w == 8 || w == 16) && rwv >= 1 && rwv <= w &&
+            (rwv & (rwv - 1)) == 0 && rg >= 1 && rg <= 64 && sl >= 1 && sl <= 8) {
+            int lps = (kl4 / 4 + sl - 1) / sl * 4;
             if (lps < 4) lps = 4;
-            if ((int64_t)(s - 1) * lps >= kl4 && s > 1) continue;  // an empty slice
-            const size_t smem = (size_t)planes * ntok * (lps * 24 + 4) * 4 + (s > 1 ? (size_t)rows_per_cta * tokpad * 4 : 0);
-            if (smem > smem_budget) continue;
-            const double ctas = (double)row_tiles * s;
-            // prefer >= 2 CTAs per SM; among those, the largest tile (least staging per row)
-            double score = ctas >= 2.0 * sms ? 1000.0 + rows_per_cta * (double)lps : ctas;
-            if (score > best_score) { best_score = score; best_rg = rg; best_s = s; }
+            const size_t need = gemv_smem_bytes(planes, ntok, tokpad, lps, w, rwv, rg);
+            if (!(sl > 1 && (int64_t)(sl - 1) * lps >= kl4) && need <= 200 * 1024) {
+                best_w = w; best_rw = rwv; best_rg = rg; best_s = sl; best_lps = lps;
+            }
         }
     }
-    if (best_score < 0.0)
-        return fail(T81B200_ELIMIT, "gemm_trit: K=%lld too large for the streaming kernel", (long long)K);
+    p.row_warps = best_rw;
     p.row_groups = best_rg;
-    p.limbs_per_slice = (kl4 / 4 + best_s - 1) / best_s * 4;
-    if (p.limbs_per_slice < 4) p.limbs_per_slice = 4;
-    const int rows_per_cta = kWarps * 16 * best_rg;
-    const size_t smem = (size_t)planes * ntok * (p.limbs_per_slice * 24 + 4) * 4 +
-                        (best_s > 1 ? (size_t)rows_per_cta * tokpad * 4 : 0);
+    p.limbs_per_slice = best_lps;
+    const size_t smem = gemv_smem_bytes(planes, ntok, tokpad, best_lps, best_w, best_rw, best_rg);
     switch (x_dtype) {
-        case T81B200_BF16: return launch_ct<__nv_bfloat16>(p, c_dtype, best_s, smem, st);
-        case T81B200_F32: return launch_ct<float>(p, c_dtype, best_s, smem, st);
-        case T81B200_F16: return launch_ct<__half>(p, c_dtype, best_s, smem, st);
+        case T81B200_BF16: return launch_ct<__nv_bfloat16>(p, c_dtype, best_w, best_s, smem, st);
+        case T81B200_F32: return launch_ct<float>(p, c_dtype, best_w, best_s, smem, st);
+        case T81B200_F16: return launch_ct<__half>(p, c_dtype, best_w, best_s, smem, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
 }

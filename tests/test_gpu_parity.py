@@ -171,7 +171,8 @@ def test_gemv_bf16_matches_oracle(dev, out_f, in_f, tokens):
     y16 = ops.gemm_trit(cuda(packed, dev), xb, M=out_f, K=in_f, layout="nk", row_scale=cuda(scale, dev),
                         bias=cuda(bias, dev))
     assert y16.dtype == torch.bfloat16
-    assert rel_err(y16.float().cpu().numpy(), want) < 1e-2  # bf16 activations: 1e-2
+    # bf16 activations: 1e-2, elementwise (the bf16 store alone rounds by up to 2^-9 of the element)
+    np.testing.assert_allclose(y16.float().cpu().numpy(), want, rtol=1e-2, atol=1e-2 * float(np.sqrt(np.mean(want ** 2))))
 
 
 @pytest.mark.parametrize("tokens", [1, 5, 16])
@@ -381,7 +382,7 @@ def test_linear_eval_forward(dev):
         else:
             packed, scale = oracle.pack_dense_matrix_absmean(w, 0.45)
         want = oracle.linear_forward(packed, scale, layer.bias.detach().cpu().numpy(), x.reshape(10, 300).cpu().numpy(), 300)
-        assert rel_err(y.reshape(10, 70).cpu().numpy(), want) < 5e-5
+        assert rel_err(y.detach().reshape(10, 70).cpu().numpy(), want) < 5e-5
         assert layer.ternary_weight is not None
         layer.train()
         assert layer.ternary_weight is None  # cache dropped, as in the reference
@@ -390,7 +391,7 @@ def test_linear_eval_forward(dev):
         assert yb.dtype == torch.bfloat16
         want_b = oracle.linear_forward(packed, scale, layer.bias.detach().cpu().numpy(),
                                        x.to(torch.bfloat16).float().reshape(10, 300).cpu().numpy(), 300)
-        assert rel_err(yb.float().reshape(10, 70).cpu().numpy(), want_b) < 1e-2
+        assert rel_err(yb.detach().float().reshape(10, 70).cpu().numpy(), want_b) < 1e-2
     with pytest.raises(ValueError, match="expects 2D or 3D inputs"):
         layer(torch.zeros(1, 2, 3, 300, device=dev))
 
