@@ -351,7 +351,7 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     const int sms = sm_count();
     const double sm_bw = 6.5e12 / sms;   // HBM share of one SM, bytes/s
     const double l2_bw = 1.0e11;         // L2 -> one SM, bytes/s (staging of activations)
-    const double issue = 4 * 0.6 * 1.7e9;  // warp instructions per second one SM sustains here
+    const double chunk_rate = 4 * 1.8e9 / 450.0;  // 4-limb chunks per second one SM sustains (measured: ~450 clk each)
     int best_w = 16, best_rw = 4, best_rg = 1, best_s = 1, best_lps = 4;
     double best_t = 1e30;
     for (int w = 8; w <= 16; w += 8)
@@ -371,9 +371,9 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
                     const double waves = ceil(ctas / sms);
                     const double stream = (double)rows_per_cta * lps * 16 / sm_bw;
                     const double chunks = (double)rwv * rg * (lps / 4.0);
-                    const double work = chunks * (150.0 + 60.0 * planes * (tokpad / 8)) / issue;
+                    const double work = chunks * (1.0 + 0.25 * (planes * (tokpad / 8) - 1)) / chunk_rate;
                     const double staging = (double)planes * ntok * lps * 96 / l2_bw;
-                    const double fixed = 1.0e-6 + (s > 1 ? 1.5e-6 : 0.0);
+                    const double fixed = 2.0e-6 + (s > 1 ? 1.0e-6 : 0.0) + (w == 16 ? 0.3e-6 : 0.0);
                     const double t = waves * (fixed + staging + (stream > work ? stream : work));
                     if (t < best_t) { best_t = t; best_w = w; best_rw = rwv; best_rg = rg; best_s = s; best_lps = lps; }
                 }
