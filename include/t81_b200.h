@@ -145,6 +145,13 @@ T81B200_API int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, cons
                       int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta,
                       void *workspace, size_t workspace_bytes, void *stream);
 
+/* TRIT mode with HOST pointers, fp32 operands, KN layout (B is (K, N), C is (M, N), both
+ * dense row-major) — the additive float-B overload of t81::linalg::gemm_ternary for C++
+ * callers that hold std::span data.  Copies in, runs, copies C back and
+ * synchronises.  Allocates device staging buffers on first use and when sizes grow. */
+T81B200_API int t81b200_gemm_trit_host(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N,
+                                       int64_t K, float alpha, float beta);
+
 /* Status word of the tensor-core kernel on the current device: 0 = no problem seen;
  * 1..4 = a bounded wait inside the kernel expired (producer, MMA issuer, epilogue,
  * converter) and that launch's output is invalid.  The kernel never spins forever:

@@ -40,7 +40,7 @@ def source_hash() -> str:
     """Hash of every source the library is built from (file times do not survive copies)."""
     import hashlib
     h = hashlib.sha256()
-    deps = sorted(os.path.join(_CSRC, f) for f in os.listdir(_CSRC))
+    deps = sorted(os.path.join(_CSRC, f) for f in os.listdir(_CSRC) if os.path.isfile(os.path.join(_CSRC, f)))
     deps.append(os.path.join(os.path.dirname(_PKG), "include", "t81_b200.h"))
     for d in deps:
         h.update(os.path.basename(d).encode())

@@ -70,8 +70,8 @@ gemm_limb_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, f
 
 struct HostStaging {
     std::mutex mu;
-    void *a = nullptr, *b = nullptr, *c = nullptr;
-    size_t a_cap = 0, b_cap = 0, c_cap = 0;
+    void *a = nullptr, *b = nullptr, *c = nullptr, *ws = nullptr;
+    size_t a_cap = 0, b_cap = 0, c_cap = 0, ws_cap = 0;
     int device = -1;
 };
 HostStaging g_staging;
@@ -114,8 +114,8 @@ extern "C" int t81b200_gemm_limb_host(const uint8_t *A, const uint8_t *B, float 
     T81_CUDA_TRY(cudaGetDevice(&dev));
     if (dev != g_staging.device) {
         // buffers belong to the device they were allocated on
-        g_staging.a = g_staging.b = g_staging.c = nullptr;
-        g_staging.a_cap = g_staging.b_cap = g_staging.c_cap = 0;
+        g_staging.a = g_staging.b = g_staging.c = g_staging.ws = nullptr;
+        g_staging.a_cap = g_staging.b_cap = g_staging.c_cap = g_staging.ws_cap = 0;
         g_staging.device = dev;
     }
     const size_t a_bytes = (size_t)M * k_limbs * 16, b_bytes = (size_t)k_limbs * N * 16, c_bytes = (size_t)M * N * 4;
@@ -127,6 +127,39 @@ extern "C" int t81b200_gemm_limb_host(const uint8_t *A, const uint8_t *B, float 
     T81_CUDA_TRY(cudaMemcpyAsync(g_staging.c, C, c_bytes, cudaMemcpyHostToDevice, 0));
     if (int rc = t81b200_gemm_limb((const uint8_t *)g_staging.a, (const uint8_t *)g_staging.b, (float *)g_staging.c,
                                    M, N, k_limbs, alpha, beta, nullptr))
+        return rc;
+    T81_CUDA_TRY(cudaMemcpyAsync(C, g_staging.c, c_bytes, cudaMemcpyDeviceToHost, 0));
+    T81_CUDA_TRY(cudaStreamSynchronize(0));
+    return T81B200_OK;
+}
+
+extern "C" int t81b200_gemm_trit_host(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N, int64_t K,
+                                      float alpha, float beta) {
+    if (M < 0 || N < 0 || K < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
+    if (int rc = check_device()) return rc;
+    if (M == 0 || N == 0) return T81B200_OK;
+    if (!C || (K > 0 && (!A || !B))) return fail(T81B200_EINVAL, "gemm_trit_host: null pointer");
+    std::lock_guard<std::mutex> lock(g_staging.mu);
+    int dev = 0;
+    T81_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != g_staging.device) {
+        g_staging.a = g_staging.b = g_staging.c = g_staging.ws = nullptr;
+        g_staging.a_cap = g_staging.b_cap = g_staging.c_cap = g_staging.ws_cap = 0;
+        g_staging.device = dev;
+    }
+    const int64_t kl = (K + 47) / 48;
+    const size_t a_bytes = (size_t)M * kl * 16, b_bytes = (size_t)K * N * 4, c_bytes = (size_t)M * N * 4;
+    const size_t ws_bytes = t81b200_gemm_trit_workspace_bytes(T81B200_F32, T81B200_LAYOUT_KN, T81B200_F32, M, N, K);
+    if (int rc = grow(&g_staging.a, &g_staging.a_cap, a_bytes ? a_bytes : 16)) return rc;
+    if (int rc = grow(&g_staging.b, &g_staging.b_cap, b_bytes ? b_bytes : 16)) return rc;
+    if (int rc = grow(&g_staging.c, &g_staging.c_cap, c_bytes)) return rc;
+    if (ws_bytes) if (int rc = grow(&g_staging.ws, &g_staging.ws_cap, ws_bytes)) return rc;
+    if (a_bytes) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.a, A, a_bytes, cudaMemcpyHostToDevice, 0));
+    if (b_bytes) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.b, B, b_bytes, cudaMemcpyHostToDevice, 0));
+    if (beta != 0.0f) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.c, C, c_bytes, cudaMemcpyHostToDevice, 0));
+    if (int rc = t81b200_gemm_trit((const uint8_t *)g_staging.a, nullptr, g_staging.b, T81B200_F32, T81B200_LAYOUT_KN, N,
+                                   nullptr, g_staging.c, T81B200_F32, N, M, N, K, alpha, beta, g_staging.ws,
+                                   g_staging.ws_cap, nullptr))
         return rc;
     T81_CUDA_TRY(cudaMemcpyAsync(C, g_staging.c, c_bytes, cudaMemcpyDeviceToHost, 0));
     T81_CUDA_TRY(cudaStreamSynchronize(0));
