@@ -78,23 +78,36 @@ __device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 v) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// d = a * b + c on two bf16 lanes, one rounding (HFMA2.BF16).  Additions are written as
+// fma(a, 1, c) on purpose: a packed bf16 *add* is not a single native instruction on
+// sm_100a (it goes through fp32 and a conversion on the quarter-rate XU pipe), the fma is.
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 __device__ __forceinline__ TrytePairTrits decode_tryte_pair(uint32_t x128) {
     // x128: lanes hold 128 + byte (bit pattern 0x4300 | byte).
-    const __nv_bfloat162 kM141 = bf162_from_bits(0xC30DC30Du);  // -141
-    const __nv_bfloat162 kNinth = bf162_from_bits(0x3DE43DE4u); // 57/512
-    const __nv_bfloat162 kThird = bf162_from_bits(0x3EAB3EABu); // 171/512
-    const __nv_bfloat162 k130 = bf162_from_bits(0x43024302u);   // 130
-    const __nv_bfloat162 kM130 = bf162_from_bits(0xC302C302u);  // -130
-    const __nv_bfloat162 kM9 = bf162_from_bits(0xC110C110u);    // -9
-    const __nv_bfloat162 kM3 = bf162_from_bits(0xC040C040u);    // -3
+    constexpr uint32_t kOne = 0x3F803F80u;    //  1
+    constexpr uint32_t kM141 = 0xC30DC30Du;   // -141
+    constexpr uint32_t kNinth = 0x3DE43DE4u;  //  57/512
+    constexpr uint32_t kThird = 0x3EAB3EABu;  //  171/512
+    constexpr uint32_t k130 = 0x43024302u;    //  130
+    constexpr uint32_t kM130 = 0xC302C302u;   // -130
+    constexpr uint32_t kM9 = 0xC110C110u;     // -9
+    constexpr uint32_t kM3 = 0xC040C040u;     // -3
+    const uint32_t v = fma_bf16x2(x128, kOne, kM141);
+    const uint32_t q = fma_bf16x2(v, kNinth, k130);
+    const uint32_t t2 = fma_bf16x2(q, kOne, kM130);
+    const uint32_t r = fma_bf16x2(t2, kM9, v);
+    const uint32_t p = fma_bf16x2(r, kThird, k130);
+    const uint32_t t1 = fma_bf16x2(p, kOne, kM130);
+    const uint32_t t0 = fma_bf16x2(t1, kM3, r);
     TrytePairTrits o;
-    const __nv_bfloat162 v = __hadd2(bf162_from_bits(x128), kM141);
-    const __nv_bfloat162 q = __hfma2(v, kNinth, k130);
-    o.t2 = __hadd2(q, kM130);
-    const __nv_bfloat162 r = __hfma2(o.t2, kM9, v);
-    const __nv_bfloat162 p = __hfma2(r, kThird, k130);
-    o.t1 = __hadd2(p, kM130);
-    o.t0 = __hfma2(o.t1, kM3, r);
+    o.t0 = bf162_from_bits(t0);
+    o.t1 = bf162_from_bits(t1);
+    o.t2 = bf162_from_bits(t2);
     return o;
 }
 
