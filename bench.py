@@ -233,8 +233,8 @@ def run_ours(args):
     out_widths = sorted({o for _, o, _ in LINEARS})
     y_loc = {o: torch.empty(ptok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths}
     yd_loc = {o: torch.empty(dtok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths}
-    y_all = {o: torch.empty(world, ptok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths} if world > 1 else None
-    yd_all = {o: torch.empty(world, dtok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths} if world > 1 else None
+    y_all = {o: torch.empty(world * ptok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths} if world > 1 else None
+    yd_all = {o: torch.empty(world * dtok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths} if world > 1 else None
     y_full = {o: torch.empty(ptok, o, dtype=torch.bfloat16, device=dev) for o in out_widths} if world > 1 else None
     yd_full = {o: torch.empty(dtok, o, dtype=torch.bfloat16, device=dev) for o in out_widths} if world > 1 else None
 
@@ -244,7 +244,7 @@ def run_ours(args):
         if world > 1:
             full = out_l * world
             dist.all_gather_into_tensor(ya[full], yl[full])
-            yf[full].view(-1, world, out_l).copy_(ya[full].permute(1, 0, 2))  # rank-major -> token-major
+            yf[full].view(-1, world, out_l).copy_(ya[full].view(world, -1, out_l).permute(1, 0, 2))  # rank-major -> token-major
 
     def prefill():
         for mods in layers:

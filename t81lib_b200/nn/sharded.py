@@ -34,8 +34,9 @@ def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     if world == 1:
         return local
     tokens, per = local.shape
-    gathered = torch.empty((world, tokens, per), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
+    flat = torch.empty((world * tokens, per), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, local.contiguous(), group=group)  # rank-major concatenation
+    gathered = flat.view(world, tokens, per)
     if tokens == 1:
         return gathered.reshape(1, world * per)
     return gathered.permute(1, 0, 2).reshape(tokens, world * per)
