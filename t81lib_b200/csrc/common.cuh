@@ -137,6 +137,22 @@ __device__ __forceinline__ void decode_limb(const uint4 &limb, uint32_t (&out)[2
     }
 }
 
+// Half a limb: two words (8 trytes) -> 12 packed registers, same order as decode_limb.
+__device__ __forceinline__ void decode_words(uint32_t w0, uint32_t w1, uint32_t (&out)[12]) {
+    const uint32_t w[2] = {w0, w1};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const TrytePairTrits a = decode_tryte_pair(tryte_pair_lo(w[i]));
+        const TrytePairTrits b = decode_tryte_pair(tryte_pair_hi(w[i]));
+        out[6 * i + 0] = bf162_bits(a.t0);
+        out[6 * i + 1] = bf162_bits(a.t1);
+        out[6 * i + 2] = bf162_bits(a.t2);
+        out[6 * i + 3] = bf162_bits(b.t0);
+        out[6 * i + 4] = bf162_bits(b.t1);
+        out[6 * i + 5] = bf162_bits(b.t2);
+    }
+}
+
 // Position inside a limb of the trit held by (register r, half h) of decode_limb.
 __host__ __device__ __forceinline__ int decoded_trit_index(int r, int h) {
     return 6 * (r / 3) + 3 * h + (r % 3);

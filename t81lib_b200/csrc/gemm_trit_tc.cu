@@ -28,13 +28,13 @@ namespace t81b200 {
 namespace {
 
 constexpr int BM = 128;          // output features per tile (UMMA M)
-constexpr int BN = 256;          // tokens per tile (UMMA N)
+constexpr int BN_MAX = 256;      // tokens per tile (UMMA N) with one activation plane; 128 with two
 constexpr int BK = 64;           // k-atom: 64 bf16 = 128 bytes
 constexpr int A_STAGES = 6;      // two super-blocks of expanded weights
 constexpr int B_STAGES = 3;
 constexpr int RAW_STAGES = 2;
 constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
-constexpr int B_STAGE_BYTES = BN * BK * 2;    // 32 KB
+constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;  // 32 KB: one 256-token plane or two 128-token planes
 constexpr int RAW_STAGE_BYTES = BM * 64;      // 4 limbs per row: 8 KB
 constexpr int NUM_THREADS = 14 * 32;
 constexpr int CONVERTER_WARP0 = 6;
@@ -44,8 +44,10 @@ constexpr int SMEM_BYTES = SMEM_DATA_BYTES + 256 /*barriers*/ + 1024 /*alignment
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
-// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N tokens, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 
 enum { STATUS_OK = 0, STATUS_TIMEOUT_PRODUCER = 1, STATUS_TIMEOUT_MMA = 2, STATUS_TIMEOUT_EPILOGUE = 3, STATUS_TIMEOUT_CONVERTER = 4 };
 
@@ -54,8 +56,10 @@ __device__ int g_tc_status = 0;
 struct TcParams {
     const float *row_scale, *bias;
     void *C;
-    int64_t ldc, M, N, K, kl;
+    int64_t c_row_stride, c_tok_stride;  // element strides of C along output features and tokens
+    int64_t M, N, K, kl;
     int m_tiles, n_tiles, n_atoms;
+    int plane_rows;  // row distance between the activation planes in the tensor map
     float alpha, beta;
 };
 
@@ -105,12 +109,13 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return d;
 }
 
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(accumulate)
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -137,9 +142,15 @@ struct Ring {
     }
 };
 
-template <typename CT>
+// PLANES = 1: bf16 activations as they are.  PLANES = 2: activations split into a bf16 "hi"
+// plane and a bf16 "lo" plane (x = hi + lo to 16 mantissa bits); both are multiplied with the
+// same expanded weights into the same accumulator, on a 128-token tile.
+template <typename CT, int PLANES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    constexpr int BN = BN_MAX / PLANES;
+    constexpr int PLANE_BYTES = BN * BK * 2;
+    constexpr uint32_t kInstrDesc = instr_desc(BN);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_smem = base;
@@ -198,7 +209,10 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         ok = mbar_wait(b_empty(b.stage), b.phase ^ 1);
                         if (!ok) break;
                         mbar_arrive_expect_tx(b_full(b.stage), B_STAGE_BYTES);
-                        tma_load_2d(b_smem + b.stage * B_STAGE_BYTES, &map_x, a * BK, n0, b_full(b.stage));
+#pragma unroll
+                        for (int pl = 0; pl < PLANES; ++pl)
+                            tma_load_2d(b_smem + b.stage * B_STAGE_BYTES + pl * PLANE_BYTES, &map_x, a * BK,
+                                        pl * p.plane_rows + n0, b_full(b.stage));
                         b.advance(B_STAGES);
                     }
                 }
@@ -217,16 +231,20 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 ok = mbar_wait(acc_empty(buf), acc_phase ^ 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN_MAX;
                 for (int at = 0; at < p.n_atoms; ++at) {
                     ok = mbar_wait(a_full(a.stage), a.phase) && mbar_wait(b_full(b.stage), b.phase);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = umma_desc(a_smem + a.stage * A_STAGE_BYTES);
-                    const uint64_t bd = umma_desc(b_smem + b.stage * B_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), (at | k) != 0 ? 1u : 0u);
+                    for (int pl = 0; pl < PLANES; ++pl) {
+                        const uint64_t bd = umma_desc(b_smem + b.stage * B_STAGE_BYTES + pl * PLANE_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), kInstrDesc,
+                                      (at | k | pl) != 0 ? 1u : 0u);
+                    }
                     umma_commit(a_empty(a.stage));
                     umma_commit(b_empty(b.stage));
                     a.advance(A_STAGES);
@@ -253,11 +271,11 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const bool row_ok = row < p.M;
             const float scale = (row_ok && p.row_scale ? p.row_scale[row] : 1.0f) * p.alpha;
             const float bias = row_ok && p.bias ? p.bias[row] : 0.0f;
-            CT *crow = static_cast<CT *>(p.C) + row;
+            CT *crow = static_cast<CT *>(p.C) + row * p.c_row_stride;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + c * 32), v);
+                tmem_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN_MAX + c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row_ok) {
 #pragma unroll
@@ -265,7 +283,7 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const int64_t tok = (int64_t)n0 + c * 32 + i;
                         if (tok < p.N) {
                             float y = __uint_as_float(v[i]) * scale + bias;
-                            CT *dst = crow + tok * p.ldc;
+                            CT *dst = crow + tok * p.c_tok_stride;
                             if (p.beta != 0.0f) y += p.beta * to_float<CT>(*dst);
                             *dst = from_float<CT>(y);
                         }
@@ -394,9 +412,9 @@ int make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, size_t elem, const voi
     return T81B200_OK;
 }
 
-template <typename CT>
+template <typename CT, int PLANES>
 int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, cudaStream_t st) {
-    auto kern = gemm_trit_tc_kernel<CT>;
+    auto kern = gemm_trit_tc_kernel<CT, PLANES>;
     static bool configured = false;
     if (!configured) {
         T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -409,17 +427,103 @@ int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, c
     return T81B200_OK;
 }
 
-}  // namespace
-
-// The tensor-core path takes bf16 activations in the token-major (NK) layout with 16-byte
-// aligned rows; everything else goes to the general kernel.
-bool gemm_trit_tc_eligible(int b_dtype, int layout, int c_dtype, int64_t M, int64_t N, int64_t K) {
-    (void)c_dtype;
-    return b_dtype == T81B200_BF16 && layout == T81B200_LAYOUT_NK && N > 16 && M >= 1 && K >= 1 &&
-           M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31);
+template <int PLANES>
+int launch_tc_ct(int c_dtype, const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, cudaStream_t st) {
+    switch (c_dtype) {
+        case T81B200_F32: return launch_tc<float, PLANES>(mw, mx, p, st);
+        case T81B200_BF16: return launch_tc<__nv_bfloat16, PLANES>(mw, mx, p, st);
+        case T81B200_F16: return launch_tc<__half, PLANES>(mw, mx, p, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
 }
 
-size_t gemm_trit_tc_workspace(int, int, int, int64_t, int64_t, int64_t) { return 0; }
+// Pre-pass for activations the TMA path cannot read directly (fp32 / fp16 values, the
+// (K, N) layout, unaligned rows): writes token-major bf16 planes into scratch memory,
+//   plane 0 = bf16(x), plane 1 = bf16(x - plane 0)      (PLANES == 2)
+// as scratch[plane][token][k], row length kpad.  32 x 32 tiles through shared memory so
+// that both the read (along n for KN, along k for NK) and the write (along k) coalesce.
+template <typename BT, int PLANES>
+__global__ void __launch_bounds__(256) stage_planes_kernel(const BT *__restrict__ B, int64_t sbk, int64_t sbn, int64_t N,
+                                                           int64_t K, __nv_bfloat16 *__restrict__ out, int64_t kpad,
+                                                           int64_t plane_elems) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const int64_t n0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
+    const bool k_fast = sbk == 1;  // NK layout: k is the contiguous index of the source
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int a = ty + 8 * i;
+        const int64_t n = k_fast ? n0 + a : n0 + tx, k = k_fast ? k0 + tx : k0 + a;
+        float v = 0.0f;
+        if (n < N && k < K) v = to_float<BT>(B[k * sbk + n * sbn]);
+        if (k_fast) tile[a][tx] = v; else tile[tx][a] = v;  // tile[n][k]
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int a = ty + 8 * i;
+        const int64_t n = n0 + a, k = k0 + tx;
+        if (n < N && k < kpad) {
+            const float v = tile[a][tx];
+            const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+            out[n * kpad + k] = hi;
+            if (PLANES == 2) out[plane_elems + n * kpad + k] = __float2bfloat16_rn(v - __bfloat162float(hi));
+        }
+    }
+}
+
+template <typename BT>
+int launch_stage(const void *B, int layout, int64_t ldb, int64_t N, int64_t K, int planes, __nv_bfloat16 *out,
+                 int64_t kpad, int64_t plane_elems, cudaStream_t st) {
+    const int64_t sbk = layout == T81B200_LAYOUT_KN ? ldb : 1, sbn = layout == T81B200_LAYOUT_KN ? 1 : ldb;
+    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((kpad + 31) / 32));
+    if (grid.y > 65535u) return fail(T81B200_ELIMIT, "gemm_trit: K too large");
+    if (planes == 2)
+        stage_planes_kernel<BT, 2><<<grid, 256, 0, st>>>(static_cast<const BT *>(B), sbk, sbn, N, K, out, kpad, plane_elems);
+    else
+        stage_planes_kernel<BT, 1><<<grid, 256, 0, st>>>(static_cast<const BT *>(B), sbk, sbn, N, K, out, kpad, plane_elems);
+    T81_LAUNCH_CHECK("stage_planes_kernel");
+    return T81B200_OK;
+}
+
+// How the dense operand reaches the tensor-core kernel.
+struct TcPlan {
+    bool direct;       // bf16, token-major: TMA reads the caller's buffer
+    int planes;        // 1 or 2
+    int bn;            // tokens per tile
+    int64_t kpad;      // scratch row length (elements)
+    int64_t rows_pad;  // scratch rows per plane (a whole number of tiles)
+    size_t scratch_bytes;
+};
+
+TcPlan make_plan(int b_dtype, int layout, int64_t N, int64_t K) {
+    TcPlan pl;
+    pl.direct = b_dtype == T81B200_BF16 && layout == T81B200_LAYOUT_NK;
+    pl.planes = b_dtype == T81B200_BF16 ? 1 : 2;
+    pl.bn = BN_MAX / pl.planes;
+    pl.kpad = (K + 7) & ~(int64_t)7;
+    pl.rows_pad = (N + pl.bn - 1) / pl.bn * pl.bn;
+    pl.scratch_bytes = pl.direct ? 0 : (size_t)pl.planes * pl.rows_pad * pl.kpad * 2;
+    return pl;
+}
+
+}  // namespace
+
+// The tensor-core path reads bf16 token-major activations in place; other dtypes and the
+// (K, N) layout go through the staging pre-pass into scratch memory first.  Small problems
+// stay on the general kernel (they are launch-bound either way).
+bool gemm_trit_tc_eligible(int b_dtype, int layout, int c_dtype, int64_t M, int64_t N, int64_t K) {
+    (void)c_dtype;
+    if (M < 1 || N < 1 || K < 1 || M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return false;
+    const bool direct = b_dtype == T81B200_BF16 && layout == T81B200_LAYOUT_NK;
+    if (direct) return N > 16;
+    return (double)M * (double)N * (double)K >= 1.6e7 && N >= 8;
+}
+
+size_t gemm_trit_tc_workspace(int b_dtype, int layout, int c_dtype, int64_t M, int64_t N, int64_t K) {
+    (void)c_dtype; (void)M;
+    return make_plan(b_dtype, layout, N, K).scratch_bytes;
+}
 
 int gemm_trit_tc_status(int reset) {
     int v = 0;
@@ -434,29 +538,45 @@ int gemm_trit_tc_status(int reset) {
 int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                         int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int64_t N,
                         int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t st) {
-    (void)workspace; (void)workspace_bytes; (void)b_dtype; (void)layout;
-    if (reinterpret_cast<uintptr_t>(B) % 16 != 0 || (ldb * 2) % 16 != 0)
-        return T81B200_EALIGN;  // caller falls back to the general kernel
+    const TcPlan plan = make_plan(b_dtype, layout, N, K);
+    const void *x_ptr = B;
+    int64_t x_ld = ldb, x_rows = N;
+    if (plan.direct) {
+        if (reinterpret_cast<uintptr_t>(B) % 16 != 0 || (ldb * 2) % 16 != 0)
+            return T81B200_EALIGN;  // caller falls back to the general kernel
+    } else {
+        if (!workspace || workspace_bytes < plan.scratch_bytes || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
+            return fail(T81B200_EWORKSPACE, "gemm_trit: %zu bytes of 16-byte aligned workspace needed, %zu given",
+                        plan.scratch_bytes, workspace_bytes);
+        __nv_bfloat16 *scratch = static_cast<__nv_bfloat16 *>(workspace);
+        const int64_t plane_elems = plan.rows_pad * plan.kpad;
+        int rc = T81B200_EINVAL;
+        switch (b_dtype) {
+            case T81B200_F32: rc = launch_stage<float>(B, layout, ldb, N, K, plan.planes, scratch, plan.kpad, plane_elems, st); break;
+            case T81B200_BF16: rc = launch_stage<__nv_bfloat16>(B, layout, ldb, N, K, plan.planes, scratch, plan.kpad, plane_elems, st); break;
+            case T81B200_F16: rc = launch_stage<__half>(B, layout, ldb, N, K, plan.planes, scratch, plan.kpad, plane_elems, st); break;
+        }
+        if (rc) return rc;
+        x_ptr = scratch; x_ld = plan.kpad; x_rows = (int64_t)plan.planes * plan.rows_pad;
+    }
     const int64_t kl = (K + 47) / 48;
     CUtensorMap mw, mx;
     if (int rc = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)kl * 16, (uint64_t)M, (uint64_t)kl * 16, 64, BM,
                              CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
-    if (int rc = make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN,
-                             CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_ptr, (uint64_t)K, (uint64_t)x_rows, (uint64_t)x_ld * 2, BK,
+                             (uint32_t)plan.bn, CU_TENSOR_MAP_SWIZZLE_128B))
         return rc;
     TcParams p;
-    p.row_scale = row_scale; p.bias = bias; p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.kl = kl;
+    p.row_scale = row_scale; p.bias = bias; p.C = C; p.M = M; p.N = N; p.K = K; p.kl = kl;
+    if (layout == T81B200_LAYOUT_NK) { p.c_row_stride = 1; p.c_tok_stride = ldc; }
+    else { p.c_row_stride = ldc; p.c_tok_stride = 1; }
     p.m_tiles = (int)((M + BM - 1) / BM);
-    p.n_tiles = (int)((N + BN - 1) / BN);
+    p.n_tiles = (int)((N + plan.bn - 1) / plan.bn);
     p.n_atoms = (int)((K + BK - 1) / BK);
+    p.plane_rows = (int)plan.rows_pad;
     p.alpha = alpha; p.beta = beta;
-    switch (c_dtype) {
-        case T81B200_F32: return launch_tc<float>(mw, mx, p, st);
-        case T81B200_BF16: return launch_tc<__nv_bfloat16>(mw, mx, p, st);
-        case T81B200_F16: return launch_tc<__half>(mw, mx, p, st);
-    }
-    return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
+    return plan.planes == 2 ? launch_tc_ct<2>(c_dtype, mw, mx, p, st) : launch_tc_ct<1>(c_dtype, mw, mx, p, st);
 }
 
 }  // namespace t81b200

@@ -30,7 +30,6 @@ namespace t81b200 {
 
 namespace {
 
-constexpr int kPrefetch = 4;  // chunks of 4 limbs in flight per lane
 
 struct GemvParams {
     const uint8_t *A;       // (M, kl, 16)
@@ -133,8 +132,12 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int64_t row, int 
 template <typename XT> struct Planes { static constexpr int value = 2; };
 template <> struct Planes<__nv_bfloat16> { static constexpr int value = 1; };
 
-template <typename XT, typename CT, int TOKB, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 1) gemv_trit_kernel(const GemvParams p) {
+// VAR 0: whole limbs decoded at once, 4 chunks in flight, one CTA per SM (up to 128 registers).
+// VAR 1: half limbs at a time, 2 chunks in flight, two CTAs per SM (64 registers): twice the
+//        resident warps to hide the latency of the dependent decode chains.
+template <typename XT, typename CT, int TOKB, int WARPS, int VAR>
+__global__ void __launch_bounds__(WARPS * 32, VAR == 1 ? (WARPS == 8 ? 4 : 2) : 1) gemv_trit_kernel(const GemvParams p) {
+    constexpr int kPrefetch = VAR == 1 ? 2 : 4;  // chunks of 4 limbs in flight per lane
     constexpr int PLANES = Planes<XT>::value;
     constexpr int THREADS = WARPS * 32;
     constexpr int kTokPad = 8 * TOKB;
@@ -216,25 +219,49 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_trit_kernel(const GemvPara
             for (int s = 0; s < kPrefetch; ++s) {
                 const int c = c0 + s;
                 if (c < c_end) {
-                    uint32_t wa[24], wb[24];
-                    decode_limb(qa[s], wa);
-                    decode_limb(qb[s], wb);
+                    const uint4 la = qa[s], lb = qb[s];
                     const int cn = c + kPrefetch;
                     if (cn < c_end) {
                         const int l = limb_of(cn);
                         qa[s] = ldg_stream(pa + l);
                         qb[s] = ldg_stream(pb + l);
                     }
+                    if constexpr (VAR == 0) {
+                        uint32_t wa[24], wb[24];
+                        decode_limb(la, wa);
+                        decode_limb(lb, wb);
 #pragma unroll
-                    for (int b = 0; b < TOKB; ++b) {
+                        for (int b = 0; b < TOKB; ++b) {
 #pragma unroll
-                        for (int pl = 0; pl < PLANES; ++pl) {
-                            const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96);
+                            for (int pl = 0; pl < PLANES; ++pl) {
+                                const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96);
 #pragma unroll
-                            for (int q = 0; q < 6; ++q) {
-                                const uint4 x = xv[q];
-                                mma_bf16_16816(acc[b], wa[4 * q], wb[4 * q], wa[4 * q + 1], wb[4 * q + 1], x.x, x.y);
-                                mma_bf16_16816(acc[b], wa[4 * q + 2], wb[4 * q + 2], wa[4 * q + 3], wb[4 * q + 3], x.z, x.w);
+                                for (int q = 0; q < 6; ++q) {
+                                    const uint4 x = xv[q];
+                                    mma_bf16_16816(acc[b], wa[4 * q], wb[4 * q], wa[4 * q + 1], wb[4 * q + 1], x.x, x.y);
+                                    mma_bf16_16816(acc[b], wa[4 * q + 2], wb[4 * q + 2], wa[4 * q + 3], wb[4 * q + 3], x.z, x.w);
+                                }
+                            }
+                        }
+                    } else {
+                        const uint32_t aw[4] = {la.x, la.y, la.z, la.w}, bw[4] = {lb.x, lb.y, lb.z, lb.w};
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {  // words 2h, 2h+1 -> decode registers 12h .. 12h+11
+                            uint32_t wa[12], wb[12];
+                            decode_words(aw[2 * h], aw[2 * h + 1], wa);
+                            decode_words(bw[2 * h], bw[2 * h + 1], wb);
+#pragma unroll
+                            for (int b = 0; b < TOKB; ++b) {
+#pragma unroll
+                                for (int pl = 0; pl < PLANES; ++pl) {
+                                    const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96 + 12 * h);
+#pragma unroll
+                                    for (int q = 0; q < 3; ++q) {
+                                        const uint4 x = xv[q];
+                                        mma_bf16_16816(acc[b], wa[4 * q], wb[4 * q], wa[4 * q + 1], wb[4 * q + 1], x.x, x.y);
+                                        mma_bf16_16816(acc[b], wa[4 * q + 2], wb[4 * q + 2], wa[4 * q + 3], wb[4 * q + 3], x.z, x.w);
+                                    }
+                                }
                             }
                         }
                     }
@@ -287,9 +314,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_trit_kernel(const GemvPara
     }
 }
 
-template <typename XT, typename CT, int TOKB, int WARPS>
+template <typename XT, typename CT, int TOKB, int WARPS, int VAR>
 int launch(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) {
-    auto kern = gemv_trit_kernel<XT, CT, TOKB, WARPS>;
+    auto kern = gemv_trit_kernel<XT, CT, TOKB, WARPS, VAR>;
     if (smem_bytes > 48 * 1024)
         T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     const int rows_per_cta = p.row_warps * 16 * p.row_groups;
@@ -309,19 +336,23 @@ int launch(const GemvParams &p, int slices, size_t smem_bytes, cudaStream_t st) 
     return T81B200_OK;
 }
 
-template <typename XT, typename CT>
+template <typename XT, typename CT, int VAR>
 int launch_tokb(const GemvParams &p, int warps, int slices, size_t smem_bytes, cudaStream_t st) {
     if (p.ntok > 8)
-        return warps == 8 ? launch<XT, CT, 2, 8>(p, slices, smem_bytes, st) : launch<XT, CT, 2, 16>(p, slices, smem_bytes, st);
-    return warps == 8 ? launch<XT, CT, 1, 8>(p, slices, smem_bytes, st) : launch<XT, CT, 1, 16>(p, slices, smem_bytes, st);
+        return warps == 8 ? launch<XT, CT, 2, 8, VAR>(p, slices, smem_bytes, st) : launch<XT, CT, 2, 16, VAR>(p, slices, smem_bytes, st);
+    return warps == 8 ? launch<XT, CT, 1, 8, VAR>(p, slices, smem_bytes, st) : launch<XT, CT, 1, 16, VAR>(p, slices, smem_bytes, st);
 }
 
 template <typename XT>
-int launch_ct(const GemvParams &p, int c_dtype, int warps, int slices, size_t smem_bytes, cudaStream_t st) {
+int launch_ct(const GemvParams &p, int c_dtype, int warps, int slices, size_t smem_bytes, int variant, cudaStream_t st) {
+    // the two-CTAs-per-SM variant is built for the bf16 -> bf16 case only (the decode hot path)
+    if constexpr (Planes<XT>::value == 1)
+        if (variant == 1 && c_dtype == T81B200_BF16)
+            return launch_tokb<XT, __nv_bfloat16, 1>(p, warps, slices, smem_bytes, st);
     switch (c_dtype) {
-        case T81B200_F32: return launch_tokb<XT, float>(p, warps, slices, smem_bytes, st);
-        case T81B200_BF16: return launch_tokb<XT, __nv_bfloat16>(p, warps, slices, smem_bytes, st);
-        case T81B200_F16: return launch_tokb<XT, __half>(p, warps, slices, smem_bytes, st);
+        case T81B200_F32: return launch_tokb<XT, float, 0>(p, warps, slices, smem_bytes, st);
+        case T81B200_BF16: return launch_tokb<XT, __nv_bfloat16, 0>(p, warps, slices, smem_bytes, st);
+        case T81B200_F16: return launch_tokb<XT, __half, 0>(p, warps, slices, smem_bytes, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
 }
@@ -352,7 +383,7 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     const double sm_bw = 6.5e12 / sms;   // HBM share of one SM, bytes/s
     const double l2_bw = 1.0e11;         // L2 -> one SM, bytes/s (staging of activations)
     const double chunk_rate = 4 * 1.8e9 / 450.0;  // 4-limb chunks per second one SM sustains (measured: ~450 clk each)
-    int best_w = 16, best_rw = 4, best_rg = 1, best_s = 1, best_lps = 4;
+    int best_w = 16, best_rw = 4, best_rg = 1, best_s = 1, best_lps = 4, variant = 0;
     double best_t = 1e30;
     for (int w = 8; w <= 16; w += 8)
         for (int rwv = 1; rwv <= w; rwv *= 2)
@@ -382,7 +413,7 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     // Tuning override: T81B200_GEMV_CFG="warps,row_warps,row_groups,slices" (used by sweeps; unset in production).
     if (const char *env = getenv("T81B200_GEMV_CFG")) {
         int w = 0, rwv = 0, rg = 0, sl = 0;
-        if (sscanf(env, "%d,%d,%d,%d", &w, &rwv, &rg, &sl) == 4 && (w == 8 || w == 16) && rwv >= 1 && rwv <= w &&
+        if (sscanf(env, "%d,%d,%d,%d,%d", &w, &rwv, &rg, &sl, &variant) >= 4 && (w == 8 || w == 16) && rwv >= 1 && rwv <= w &&
             (rwv & (rwv - 1)) == 0 && rg >= 1 && rg <= 64 && sl >= 1 && sl <= 8) {
             int lps = (kl4 / 4 + sl - 1) / sl * 4;
             if (lps < 4) lps = 4;
@@ -397,9 +428,9 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     p.limbs_per_slice = best_lps;
     const size_t smem = gemv_smem_bytes(planes, ntok, tokpad, best_lps, best_w, best_rw, best_rg);
     switch (x_dtype) {
-        case T81B200_BF16: return launch_ct<__nv_bfloat16>(p, c_dtype, best_w, best_s, smem, st);
-        case T81B200_F32: return launch_ct<float>(p, c_dtype, best_w, best_s, smem, st);
-        case T81B200_F16: return launch_ct<__half>(p, c_dtype, best_w, best_s, smem, st);
+        case T81B200_BF16: return launch_ct<__nv_bfloat16>(p, c_dtype, best_w, best_s, smem, variant, st);
+        case T81B200_F32: return launch_ct<float>(p, c_dtype, best_w, best_s, smem, variant, st);
+        case T81B200_F16: return launch_ct<__half>(p, c_dtype, best_w, best_s, smem, variant, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
 }

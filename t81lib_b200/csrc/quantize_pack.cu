@@ -1,17 +1,16 @@
 // Fused threshold-quantise + trit-pack kernel, and its inverse.
 //
-// One CTA of 256 threads owns one matrix row at a time.
-//   ABSMEAN pass: every thread sums |w| of the float4 groups it owns in fp64,
-//   in a fixed element order (group 4*(lane + 256*i), i ascending), then the 256
-//   partials are folded by a fixed halving tree (inside each warp, then across
-//   the 8 warps), so the row scale — and with it every trit — is reproducible
-//   bit for bit.
-//   Quantise pass: the same float4 groups (kept in registers when the row has at
-//   most 4096 columns, re-read through L1/L2 otherwise) become digits d = t+1 in
-//   a byte array in shared memory; then each thread turns 12 digits (3 words)
-//   into 4 tryte bytes and stores one 32-bit word, so the packed row leaves in
-//   fully coalesced stores.  HBM traffic is the algorithmic minimum: each weight
-//   is read from DRAM once, each packed byte written once.
+// One warp owns one matrix row at a time; nothing synchronises wider than a warp.
+//   ABSMEAN pass: |w| is summed in fp64 in a fixed order — 256 partials, partial l taking
+//   the float4 groups l, l+256, ... — which a warp reproduces with 8 accumulators per lane;
+//   the partials are folded by a fixed halving tree (32 consecutive partials = the 32 lanes
+//   of one accumulator slot, then the 8 slot sums).  The row scale, and with it every trit,
+//   is therefore reproducible bit for bit and independent of the launch shape.
+//   Quantise pass: 768 weights (16 limbs) per step: six coalesced float4 loads per lane
+//   become digits d = t+1 in a 768-byte per-warp array in shared memory, then every lane
+//   turns 12 digits into 4 tryte bytes and the warp stores 2 x 128 contiguous bytes.
+//   With the absmean rule the row is read twice; the second read is served by L1/L2 (a row
+//   is 16 KB), so DRAM sees each weight once and each packed byte once.
 #include "common.cuh"
 
 namespace t81b200 {
@@ -19,7 +18,6 @@ namespace t81b200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kRegGroups = 4;  // float4 groups per thread cached in registers
 
 // Reference rule: clamp to [-1,1], inclusive compares, NaN -> 0.  Returns t+1.
 __device__ __forceinline__ uint32_t quantize_digit(float v, float thr) {
@@ -54,128 +52,107 @@ __device__ __forceinline__ void load_group(const T *row, int64_t base, int64_t c
     }
 }
 
+constexpr int kWarpsPerCta = kThreads / 32;
+constexpr int kChunkGroups = 192;  // float4 groups per warp step: 768 weights = 16 limbs
+
+// One warp owns one row at a time; there is no block-wide barrier anywhere.
 template <typename T, bool ABSMEAN>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_t ld, float thr,
                      uint8_t *__restrict__ packed, float *__restrict__ row_scale, bool vec) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint32_t *digits = reinterpret_cast<uint32_t *>(smem);  // one byte per trit, kl*48 bytes
-    __shared__ double warp_sum[kThreads / 32];
-    __shared__ float inv_shared;
-
-    const int tid = threadIdx.x;
+    __shared__ uint32_t digit_smem[kWarpsPerCta][kChunkGroups];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t *digits = digit_smem[warp];
     const int64_t kl = (cols + 47) / 48;
-    const int64_t groups = (cols + 3) / 4;       // float4 groups holding data
-    const int64_t digit_words = kl * 12;         // 48 digits = 12 words per limb
-    const bool cached = groups <= (int64_t)kThreads * kRegGroups;
+    const int64_t groups = (cols + 3) / 4;  // float4 groups holding data
+    const int64_t out_words = kl * 4;       // 32-bit words of the packed row
+    const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerCta + warp;
+    const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerCta;
 
-    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    for (int64_t r = warp_global; r < rows; r += warp_stride) {
         const T *row = w + r * ld;
-        float reg[kRegGroups][4];
-        if (cached) {
-#pragma unroll
-            for (int i = 0; i < kRegGroups; ++i) {
-                const int64_t g = tid + (int64_t)kThreads * i;
-                if (g < groups) load_group<T>(row, 4 * g, cols, vec, reg[i]);
-                else { reg[i][0] = reg[i][1] = reg[i][2] = reg[i][3] = 0.0f; }
-            }
-        }
-
         float inv = 1.0f;
         if constexpr (ABSMEAN) {
-            double s = 0.0;
-            if (cached) {
+            // Partial l = g % 256 of the reference order lives in lane l % 32, slot l / 32:
+            // this lane's m-th group (g = lane + 32 m) belongs to slot m % 8.
+            double part[8];
 #pragma unroll
-                for (int i = 0; i < kRegGroups; ++i) {
-                    const int64_t g = tid + (int64_t)kThreads * i;
+            for (int j = 0; j < 8; ++j) part[j] = 0.0;
+            for (int64_t g0 = lane; g0 < groups; g0 += 256) {
+                float v[8][4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int64_t g = g0 + 32 * j;
+                    if (g < groups) load_group<T>(row, 4 * g, cols, vec, v[j]);
+                    else { v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.0f; }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int64_t g = g0 + 32 * j;
                     if (g < groups) {
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
-                            if (4 * g + c < cols) s += (double)fabsf(reg[i][c]);
+                            if (4 * g + c < cols) part[j] += (double)fabsf(v[j][c]);
                     }
                 }
-            } else {
-                for (int64_t g = tid; g < groups; g += kThreads) {
-                    float v[4];
-                    load_group<T>(row, 4 * g, cols, vec, v);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (4 * g + c < cols) s += (double)fabsf(v[c]);
-                }
             }
+            // halving tree inside each group of 32 consecutive partials (= the 32 lanes of slot j)
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
-            if ((tid & 31) == 0) warp_sum[tid >> 5] = s;
-            __syncthreads();
-            if (tid == 0) {
-                double g8[kThreads / 32];
+            for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int j = 0; j < kThreads / 32; ++j) g8[j] = warp_sum[j];
+                for (int off = 16; off >= 1; off >>= 1) part[j] += __shfl_down_sync(0xffffffffu, part[j], off);
+            // then over the 8 group sums (offsets 4, 2, 1); only lane 0 holds valid sums
 #pragma unroll
-                for (int off = kThreads / 64; off >= 1; off >>= 1)
+            for (int off = 4; off >= 1; off >>= 1)
 #pragma unroll
-                    for (int j = 0; j < off; ++j) g8[j] += g8[j + off];
-                const float sr = (float)(g8[0] / (double)cols);
-                inv_shared = sr > 0.0f ? __fdiv_rn(1.0f, sr) : 0.0f;
-                row_scale[r] = sr;
-            }
-            __syncthreads();
-            inv = inv_shared;
+                for (int j = 0; j < off; ++j) part[j] += part[j + off];
+            float sr = (float)(part[0] / (double)cols);
+            sr = __shfl_sync(0xffffffffu, sr, 0);
+            inv = sr > 0.0f ? __fdiv_rn(1.0f, sr) : 0.0f;
+            if (lane == 0) row_scale[r] = sr;
         }
 
-        // digits into shared memory, one 32-bit word (4 digits) per float4 group
-        if (cached) {
+        uint32_t *out = reinterpret_cast<uint32_t *>(packed + r * kl * 16);
+        for (int64_t gbase = 0; gbase < kl * 12; gbase += kChunkGroups) {
+            float v[6][4];
 #pragma unroll
-            for (int i = 0; i < kRegGroups; ++i) {
-                const int64_t g = tid + (int64_t)kThreads * i;
-                if (g < digit_words) {
-                    uint32_t word = 0x01010101u;
-                    if (g < groups) {
-                        word = 0;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const float x = ABSMEAN ? __fmul_rn(reg[i][c], inv) : reg[i][c];
-                            const uint32_t d = 4 * g + c < cols ? quantize_digit(x, thr) : 1u;
-                            word |= d << (8 * c);
-                        }
-                    }
-                    digits[g] = word;
-                }
+            for (int q = 0; q < 6; ++q) {
+                const int64_t g = gbase + lane + 32 * q;
+                if (g < groups) load_group<T>(row, 4 * g, cols, vec, v[q]);
+                else { v[q][0] = v[q][1] = v[q][2] = v[q][3] = 0.0f; }
             }
-            // the zero tail of the last limb can reach past the register-cached groups
-            for (int64_t g = tid + (int64_t)kThreads * kRegGroups; g < digit_words; g += kThreads)
-                digits[g] = 0x01010101u;
-        } else {
-            for (int64_t g = tid; g < digit_words; g += kThreads) {
-                uint32_t word = 0x01010101u;
+#pragma unroll
+            for (int q = 0; q < 6; ++q) {
+                const int64_t g = gbase + lane + 32 * q;
+                uint32_t word = 0x01010101u;  // zero trits: the tail of the last limb
                 if (g < groups) {
-                    float v[4];
-                    load_group<T>(row, 4 * g, cols, vec, v);
                     word = 0;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        const float x = ABSMEAN ? __fmul_rn(v[c], inv) : v[c];
+                        const float x = ABSMEAN ? __fmul_rn(v[q][c], inv) : v[q][c];
                         const uint32_t d = 4 * g + c < cols ? quantize_digit(x, thr) : 1u;
                         word |= d << (8 * c);
                     }
                 }
-                digits[g] = word;
+                digits[lane + 32 * q] = word;
             }
+            __syncwarp();
+            // 12 digits (3 words) -> 4 tryte bytes (1 word); 64 output words per step
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int o = lane + 32 * h;
+                const int64_t q = gbase / 3 + o;
+                if (q < out_words) {
+                    const uint32_t a = digits[3 * o], b = digits[3 * o + 1], c = digits[3 * o + 2];
+                    const uint32_t y0 = (a & 0xff) + 3u * ((a >> 8) & 0xff) + 9u * ((a >> 16) & 0xff);
+                    const uint32_t y1 = (a >> 24) + 3u * (b & 0xff) + 9u * ((b >> 8) & 0xff);
+                    const uint32_t y2 = ((b >> 16) & 0xff) + 3u * (b >> 24) + 9u * (c & 0xff);
+                    const uint32_t y3 = ((c >> 8) & 0xff) + 3u * ((c >> 16) & 0xff) + 9u * (c >> 24);
+                    out[q] = y0 | (y1 << 8) | (y2 << 16) | (y3 << 24);
+                }
+            }
+            __syncwarp();  // digits[] is reused by the next step
         }
-        __syncthreads();
-
-        // 12 digits (3 words) -> 4 tryte bytes (1 word); word index q covers trytes 4q..4q+3
-        uint32_t *out = reinterpret_cast<uint32_t *>(packed + r * kl * 16);
-        for (int64_t q = tid; q < kl * 4; q += kThreads) {
-            const uint32_t a = digits[3 * q], b = digits[3 * q + 1], c = digits[3 * q + 2];
-            // digit bytes: a = d0 d1 d2 d3, b = d4 d5 d6 d7, c = d8 d9 d10 d11
-            const uint32_t y0 = (a & 0xff) + 3u * ((a >> 8) & 0xff) + 9u * ((a >> 16) & 0xff);
-            const uint32_t y1 = (a >> 24) + 3u * (b & 0xff) + 9u * ((b >> 8) & 0xff);
-            const uint32_t y2 = ((b >> 16) & 0xff) + 3u * (b >> 24) + 9u * (c & 0xff);
-            const uint32_t y3 = ((c >> 8) & 0xff) + 3u * ((c >> 16) & 0xff) + 9u * (c >> 24);
-            out[q] = y0 | (y1 << 8) | (y2 << 16) | (y3 << 24);
-        }
-        __syncthreads();  // digits[] is reused by the next row
     }
 }
 
@@ -208,15 +185,11 @@ __global__ void unpack_kernel(const uint8_t *__restrict__ packed, int64_t rows, 
 template <typename T>
 int launch_quantize_pack(const void *w, int64_t rows, int64_t cols, int64_t ld, float thr, int rule,
                          uint8_t *packed, float *row_scale, cudaStream_t st) {
-    const int64_t kl = (cols + 47) / 48;
-    const size_t smem = (size_t)kl * 48;
-    if (smem > 200 * 1024) return fail(T81B200_ELIMIT, "quantize_pack: cols=%lld exceeds %d", (long long)cols, 200 * 1024);
     const bool vec = (reinterpret_cast<uintptr_t>(w) % (4 * sizeof(T)) == 0) && (ld % 4 == 0);
-    const int grid = (int)(rows < (int64_t)sm_count() * 16 ? rows : (int64_t)sm_count() * 16);
+    const int64_t ctas = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int grid = (int)(ctas < (int64_t)sm_count() * 8 ? ctas : (int64_t)sm_count() * 8);
     auto kern = rule == T81B200_RULE_ABSMEAN ? quantize_pack_kernel<T, true> : quantize_pack_kernel<T, false>;
-    if (smem > 48 * 1024)
-        T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(static_cast<const T *>(w), rows, cols, ld, thr, packed, row_scale, vec);
+    kern<<<grid, kThreads, 0, st>>>(static_cast<const T *>(w), rows, cols, ld, thr, packed, row_scale, vec);
     T81_LAUNCH_CHECK("quantize_pack_kernel");
     return T81B200_OK;
 }

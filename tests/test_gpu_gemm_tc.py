@@ -106,3 +106,64 @@ def test_prefill_shape_linearity_at_full_size(dev):
     got = yb[toks.to(dev)][:, rows.to(dev)].cpu().numpy()
     assert rel_err(got, want) < 2e-5
     assert _capi.kernel_status(reset=True) == 0
+
+
+# ---- activations that need the staging pre-pass (scratch workspace): fp32 / fp16 values, (K, N) layout
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("out_f,in_f,tokens", [(384, 1000, 200), (130, 70, 300), (512, 4096, 129)])
+def test_tc_gemm_staged_activations_token_major(dev, dtype, out_f, in_f, tokens):
+    from t81lib_b200 import _capi, ops
+    rng = np.random.default_rng(out_f + in_f + tokens)
+    packed, scale, x, bias = case(rng, out_f, in_f, tokens)
+    xd = cuda(x, dev, dtype)
+    oracle.set_num_threads(8)
+    want = oracle.linear_forward(packed, scale, bias, xd.float().cpu().numpy(), in_f)
+    oracle.set_num_threads(1)
+    assert _capi.lib.t81b200_gemm_trit_workspace_bytes(_capi.F32 if dtype == torch.float32 else _capi.F16,
+                                                        _capi.LAYOUT_NK, _capi.F32, out_f, tokens, in_f) > 0
+    y = ops.gemm_trit(cuda(packed, dev), xd, M=out_f, K=in_f, layout="nk", row_scale=cuda(scale, dev),
+                      bias=cuda(bias, dev), out_dtype=torch.float32)
+    assert _capi.kernel_status(reset=True) == 0
+    # two bf16 planes carry 16 mantissa bits of each activation: 1e-3 asked for fp32, ~1e-5 achieved
+    assert rel_err(y.cpu().numpy(), want) < 1e-3
+    assert rel_err(y.cpu().numpy(), want) < 5e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_tc_gemm_reference_argument_order(dev, dtype):
+    """(K, N) dense operand and (M, N) result, the layout of t81::linalg::gemm_ternary."""
+    from t81lib_b200 import _capi, ops
+    rng = np.random.default_rng(77)
+    M, N, K = 300, 260, 1000
+    trits = rng.integers(-1, 2, (M, K)).astype(np.int8)
+    A = oracle.pack_trits_rowwise(trits)
+    B = cuda(rng.normal(size=(K, N)).astype(np.float32), dev, dtype)
+    C0 = rng.normal(size=(M, N)).astype(np.float32)
+    oracle.set_num_threads(8)
+    want = oracle.gemm_trit(A, B.float().cpu().numpy(), C0, M, N, K, 1.5, 0.5)
+    oracle.set_num_threads(1)
+    C = cuda(C0, dev)
+    ops.gemm_trit(cuda(A, dev), B, M=M, K=K, layout="kn", C=C, alpha=1.5, beta=0.5)
+    assert _capi.kernel_status(reset=True) == 0
+    assert rel_err(C.cpu().numpy(), want) < 5e-5
+
+
+def test_host_pointer_entry_point(dev):
+    """t81b200_gemm_trit_host: what the C++ span overload of gemm_ternary binds to."""
+    import ctypes
+    from t81lib_b200 import _capi
+    rng = np.random.default_rng(78)
+    M, N, K = 128, 64, 480
+    trits = rng.integers(-1, 2, (M, K)).astype(np.int8)
+    A = oracle.pack_trits_rowwise(trits)
+    B = rng.normal(size=(K, N)).astype(np.float32)
+    C = rng.normal(size=(M, N)).astype(np.float32)
+    want = oracle.gemm_trit(A, B, C, M, N, K, 2.0, -1.0)
+    vp = ctypes.c_void_p
+    rc = _capi.lib.t81b200_gemm_trit_host(A.ctypes.data_as(vp), B.ctypes.data_as(vp), C.ctypes.data_as(vp), M, N, K, 2.0, -1.0)
+    assert rc == 0, _capi.last_error()
+    assert rel_err(C, want) < 5e-5
+    rc = _capi.lib.t81b200_gemm_trit_host(A.ctypes.data_as(vp), B.ctypes.data_as(vp), C.ctypes.data_as(vp), -1, N, K, 1.0, 0.0)
+    assert rc == _capi.EINVAL and "non-negative" in _capi.last_error()
