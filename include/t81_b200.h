@@ -152,6 +152,28 @@ T81B200_API int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, cons
 T81B200_API int t81b200_gemm_trit_host(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N,
                                        int64_t K, float alpha, float beta);
 
+/* t81b200_gemm_trit for callers that must not allocate device memory and have none to lend:
+ * plugin hosts and inference servers whose memory pool is fixed once start-up ends, code that
+ * runs while a stream is being captured (cudaMalloc is not allowed there), and language
+ * bindings that only forward pointers they were given.  Same arguments as t81b200_gemm_trit
+ * without the workspace: the scratch that fp32 / fp16 activations and the (K, N) layout need
+ * (t81b200_gemm_trit_workspace_bytes) lives in a buffer of T81B200_STATIC_SCRATCH_BYTES that is
+ * built into the library's device image, so every GPU that loads the library carries those
+ * bytes until the process ends.  Calls that need more fail with T81B200_ELIMIT and do nothing.
+ *   - No cudaMalloc / cudaFree or other allocating call is made, on any call.
+ *   - The first call on each device looks the buffer's address up (cudaGetSymbolAddress, with
+ *     that device current); make that first call before starting a stream capture.
+ *   - All calls on a device share the one buffer.  It is fully rewritten by each call that
+ *     uses it (nothing in it has to start at zero), so calls may follow one another freely on
+ *     one stream, but two calls whose kernels can overlap on the GPU (different streams, no
+ *     dependency) race on it and must be ordered by the caller.
+ * This entry point has no counterpart in the reference. */
+#define T81B200_STATIC_SCRATCH_BYTES (16u << 20)
+T81B200_API int t81b200_gemm_trit_static(const uint8_t *A, const float *row_scale, const void *B, int b_dtype,
+                                         int layout, int64_t ldb, const float *bias, void *C, int c_dtype,
+                                         int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta,
+                                         void *stream);
+
 /* Status word of the tensor-core kernel on the current device: 0 = no problem seen;
  * 1..4 = a bounded wait inside the kernel expired (producer, MMA issuer, epilogue,
  * converter) and that launch's output is invalid.  The kernel never spins forever:

@@ -16,11 +16,12 @@ OK, EINVAL, ENODEVICE, ECUDA, EWORKSPACE, EALIGN, ELIMIT = 0, -1, -2, -3, -4, -5
 F32, BF16, F16 = 0, 1, 2
 RULE_FIXED, RULE_ABSMEAN = 0, 1
 LAYOUT_KN, LAYOUT_NK = 0, 1
+STATIC_SCRATCH_BYTES = 16 << 20
 
 EXPORTS = (
     "t81b200_device_available", "t81b200_last_error", "t81b200_version", "t81b200_quantize_pack",
     "t81b200_quantize_trits", "t81b200_unpack", "t81b200_gemm_limb", "t81b200_gemm_limb_host",
-    "t81b200_gemm_trit", "t81b200_gemm_trit_host", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
+    "t81b200_gemm_trit", "t81b200_gemm_trit_host", "t81b200_gemm_trit_static", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
 )
 
 
@@ -54,6 +55,7 @@ def _load() -> ctypes.CDLL:
     lib.t81b200_gemm_limb_host.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32]
     lib.t81b200_gemm_trit.argtypes = [vp, vp, vp, ci, ci, i64, vp, vp, ci, i64, i64, i64, i64, f32, f32,
                                       vp, ctypes.c_size_t, vp]
+    lib.t81b200_gemm_trit_static.argtypes = [vp, vp, vp, ci, ci, i64, vp, vp, ci, i64, i64, i64, i64, f32, f32, vp]
     lib.t81b200_gemm_trit_host.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32]
     lib.t81b200_gemm_trit_workspace_bytes.argtypes = [ci, ci, ci, i64, i64, i64]
     lib.t81b200_gemm_trit_workspace_bytes.restype = ctypes.c_size_t

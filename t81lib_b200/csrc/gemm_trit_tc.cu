@@ -23,6 +23,8 @@
 
 #include <cuda.h>
 
+#include <mutex>
+
 namespace t81b200 {
 
 namespace {
@@ -580,3 +582,49 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
 }
 
 }  // namespace t81b200
+
+// ---- entry point that allocates nothing -------------------------------------------------
+
+namespace {
+
+// Scratch for the staging pre-pass of t81b200_gemm_trit_static.  It is part of the loaded
+// module: every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[T81B200_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address;
+// the address the kernels need is looked up once per device, with that device current.
+void *g_static_scratch_ptr[64] = {nullptr};
+std::mutex g_static_scratch_mu;
+
+int static_scratch_address(void **out) {
+    int dev = 0;
+    T81_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return t81b200::fail(T81B200_ELIMIT, "gemm_trit_static: device index %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (!g_static_scratch_ptr[dev]) {
+        void *ptr = nullptr;
+        T81_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return T81B200_OK;
+}
+
+}  // namespace
+
+extern "C" int t81b200_gemm_trit_static(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
+                                        int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
+                                        int64_t N, int64_t K, float alpha, float beta, void *stream) {
+    if (int rc = t81b200::check_device()) return rc;
+    const size_t need = t81b200_gemm_trit_workspace_bytes(b_dtype, layout, c_dtype, M, N, K);
+    if (need > (size_t)T81B200_STATIC_SCRATCH_BYTES)
+        return t81b200::fail(T81B200_ELIMIT,
+                             "gemm_trit_static: this call needs %zu bytes of scratch, the built-in buffer holds %zu; "
+                             "use t81b200_gemm_trit with a caller-provided workspace",
+                             need, (size_t)T81B200_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    return t81b200_gemm_trit(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, scratch,
+                             (size_t)T81B200_STATIC_SCRATCH_BYTES, stream);
+}
+
