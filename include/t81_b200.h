@@ -175,8 +175,9 @@ T81B200_API int t81b200_gemm_trit_static(const uint8_t *A, const float *row_scal
                                          void *stream);
 
 /* Status word of the tensor-core kernel on the current device: 0 = no problem seen;
- * 1..4 = a bounded wait inside the kernel expired (producer, MMA issuer, epilogue,
- * converter) and that launch's output is invalid.  The kernel never spins forever:
+ * 1..4 = a bounded wait inside the tensor-core kernel expired (producer, MMA issuer,
+ * epilogue, converter), 5..6 = inside the streaming kernel (producer, consumer); that
+ * launch's output is invalid.  The kernel never spins forever:
  * every wait has an iteration limit after which it records the code, releases its
  * tensor memory and returns.  Reading the word synchronises the device; `reset`
  * non-zero clears it.  No counterpart in the reference (its CUDA path has no

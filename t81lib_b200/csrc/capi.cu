@@ -1,6 +1,7 @@
 // C ABI glue: error state, device probing and the TRIT-mode dispatcher.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -81,6 +82,7 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
                         cudaStream_t st);
 
 int gemm_trit_tc_status(int reset);
+int gemv_trit_status(int reset);
 
 }  // namespace t81b200
 
@@ -88,7 +90,9 @@ using namespace t81b200;
 
 extern "C" int t81b200_kernel_status(int reset) {
     if (int rc = check_device()) return rc;
-    return gemm_trit_tc_status(reset);
+    const int tc = gemm_trit_tc_status(reset);
+    const int gv = gemv_trit_status(reset);
+    return tc != 0 ? tc : gv;
 }
 
 extern "C" const char *t81b200_last_error(void) { return g_error; }
@@ -124,7 +128,10 @@ extern "C" int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool a_aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0;
 
-    if (a_aligned && layout == T81B200_LAYOUT_NK && N <= 16 && K > 0)
+    // T81B200_SMALLN_PATH=tc sends token counts <= 16 to the tensor-core kernel too (A/B runs).
+    const char *small_n = getenv("T81B200_SMALLN_PATH");
+    const bool small_n_tc = small_n && small_n[0] == 't' && b_dtype == T81B200_BF16;
+    if (a_aligned && layout == T81B200_LAYOUT_NK && N <= 16 && K > 0 && !small_n_tc)
         return gemv_trit_launch(A, row_scale, B, b_dtype, ldb, bias, C, c_dtype, ldc, M, (int)N, K, alpha, beta, st);
 
     if (a_aligned && gemm_trit_tc_eligible(b_dtype, layout, c_dtype, M, N, K)) {

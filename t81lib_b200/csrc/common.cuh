@@ -153,6 +153,40 @@ __device__ __forceinline__ void decode_words(uint32_t w0, uint32_t w1, uint32_t 
     }
 }
 
+// One 32-bit word of each of two limbs (4 + 4 trytes) -> 6 + 6 packed registers, in the order
+// of decode_limb (registers 6w .. 6w+5 of word w).  The four tryte-pair chains are written
+// step by step side by side and kept in program order (volatile), so that an in-order warp
+// always has four independent FMAs to issue and the MMAs that follow each word can run on
+// the tensor pipe while the next word is being decoded.
+__device__ __forceinline__ uint32_t fma_bf16x2_ordered(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm volatile("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ void decode_word_pair(uint32_t wa, uint32_t wb, uint32_t (&oa)[6], uint32_t (&ob)[6]) {
+    constexpr uint32_t kOne = 0x3F803F80u, kM141 = 0xC30DC30Du, kNinth = 0x3DE43DE4u, kThird = 0x3EAB3EABu;
+    constexpr uint32_t k130 = 0x43024302u, kM130 = 0xC302C302u, kM9 = 0xC110C110u, kM3 = 0xC040C040u;
+    uint32_t x[4] = {tryte_pair_lo(wa), tryte_pair_hi(wa), tryte_pair_lo(wb), tryte_pair_hi(wb)};
+    uint32_t v[4], q[4], t2[4], r[4], pp[4], t1[4], t0[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = fma_bf16x2_ordered(x[i], kOne, kM141);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = fma_bf16x2_ordered(v[i], kNinth, k130);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t2[i] = fma_bf16x2_ordered(q[i], kOne, kM130);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = fma_bf16x2_ordered(t2[i], kM9, v[i]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pp[i] = fma_bf16x2_ordered(r[i], kThird, k130);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t1[i] = fma_bf16x2_ordered(pp[i], kOne, kM130);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t0[i] = fma_bf16x2_ordered(t1[i], kM3, r[i]);
+    oa[0] = t0[0]; oa[1] = t1[0]; oa[2] = t2[0]; oa[3] = t0[1]; oa[4] = t1[1]; oa[5] = t2[1];
+    ob[0] = t0[2]; ob[1] = t1[2]; ob[2] = t2[2]; ob[3] = t0[3]; ob[4] = t1[3]; ob[5] = t2[3];
+}
+
 // Position inside a limb of the trit held by (register r, half h) of decode_limb.
 __host__ __device__ __forceinline__ int decoded_trit_index(int r, int h) {
     return 6 * (r / 3) + 3 * h + (r % 3);

@@ -20,8 +20,7 @@
 // Every mbarrier wait is bounded; on expiry the role records a status code and all roles
 // fall through to the common teardown (TMEM is always released).
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tma.cuh"
 
 #include <mutex>
 
@@ -44,7 +43,6 @@ constexpr int CONVERTER_WARPS = 8;
 constexpr int SMEM_DATA_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + RAW_STAGES * RAW_STAGE_BYTES;
 constexpr int SMEM_BYTES = SMEM_DATA_BYTES + 256 /*barriers*/ + 1024 /*alignment slack*/;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 // kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N tokens, M = 128.
 __host__ __device__ constexpr uint32_t instr_desc(int bn) {
@@ -64,41 +62,6 @@ struct TcParams {
     int plane_rows;  // row distance between the activation planes in the tensor map
     float alpha, beta;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait: false when the phase did not complete within the spin limit.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if (spin > 1024) __nanosleep(64);
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
 
 // K-major, SWIZZLE_128B shared-memory descriptor: rows are 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -136,13 +99,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
 }
 
-struct Ring {
-    int stage = 0;
-    uint32_t phase = 0;
-    __device__ __forceinline__ void advance(int stages) {
-        if (++stage == stages) { stage = 0; phase ^= 1; }
-    }
-};
 
 // PLANES = 1: bf16 activations as they are.  PLANES = 2: activations split into a bf16 "hi"
 // plane and a bf16 "lo" plane (x = hi + lo to 16 mantissa bits); both are multiplied with the
@@ -379,41 +335,6 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
-// ---- host: tensor maps through the driver entry point (no link-time libcuda dependency) ----
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
-int make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, size_t elem, const void *ptr, uint64_t inner, uint64_t outer,
-                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return fail(T81B200_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {row_stride_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    (void)elem;
-    CUresult rc = fn(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS) return fail(T81B200_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)rc);
-    return T81B200_OK;
-}
-
 template <typename CT, int PLANES>
 int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, cudaStream_t st) {
     auto kern = gemm_trit_tc_kernel<CT, PLANES>;
@@ -518,7 +439,7 @@ bool gemm_trit_tc_eligible(int b_dtype, int layout, int c_dtype, int64_t M, int6
     (void)c_dtype;
     if (M < 1 || N < 1 || K < 1 || M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return false;
     const bool direct = b_dtype == T81B200_BF16 && layout == T81B200_LAYOUT_NK;
-    if (direct) return N > 16;
+    if (direct) return N >= 1;  // the dispatcher sends N <= 16 to the streaming kernel first
     return (double)M * (double)N * (double)K >= 1.6e7 && N >= 8;
 }
 

@@ -18,6 +18,7 @@
 //   MMA is free as long as both operands agree, so the activations are staged in
 //   shared memory already permuted into the register order decode_limb produces.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <cooperative_groups.h>
 
@@ -357,10 +358,308 @@ int launch_ct(const GemvParams &p, int c_dtype, int warps, int slices, size_t sm
     return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
 }
 
+// ---------------------------------------------------------------------------------------------
+// TMA-fed variant.  The register-prefetch kernel above keeps at most a few KB per warp in
+// flight, and measured throughput follows bytes-in-flight / latency, far below HBM speed.
+// Here one producer thread streams the weight tile (16*RW rows x 64 bytes = one 4-limb chunk
+// per row) through a deep shared-memory ring with cp.async.bulk.tensor, so the bytes in flight
+// per SM are set by the ring size (tens of KB), not by registers.  16 consumer warps
+// (RW row groups x KW interleaved K slices: warp (rw, kw) takes chunks kw, kw+KW, ...) read
+// their two limbs per chunk with conflict-free 128-bit shared loads, release the slot at once,
+// and decode / multiply exactly as above.
+// ---------------------------------------------------------------------------------------------
+
+constexpr int kTmaConsumerWarps = 16;
+constexpr int kTmaThreads = (kTmaConsumerWarps + 1) * 32;
+constexpr int kTmaMaxStages = 48;
+
+enum { GEMV_STATUS_OK = 0, GEMV_STATUS_TIMEOUT_PRODUCER = 5, GEMV_STATUS_TIMEOUT_CONSUMER = 6 };
+__device__ int g_gemv_status = 0;
+
+struct GemvTmaParams {
+    GemvParams g;
+    int stages;        // ring depth
+    int stage_bytes;   // 16*RW*64
+    int ring_offset;   // bytes from the start of dynamic shared memory (128-byte aligned)
+    int part_offset;   // bytes: partial sums, KW x rows x tokpad floats
+    int bar_offset;    // bytes: full[stages], empty[stages]
+};
+
+template <typename XT, typename CT, int TOKB>
+__global__ void __launch_bounds__(kTmaThreads, 1)
+gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaParams tp) {
+    constexpr int PLANES = Planes<XT>::value;
+    constexpr int kTokPad = 8 * TOKB;
+    constexpr int CONSUMER_THREADS = kTmaConsumerWarps * 32;
+    const GemvParams &p = tp.g;
+    extern __shared__ __align__(128) uint8_t smem_bytes_tma[];
+    uint32_t *xs = reinterpret_cast<uint32_t *>(smem_bytes_tma);
+    float *part = reinterpret_cast<float *>(smem_bytes_tma + tp.part_offset);
+    const uint32_t ring = smem_u32(smem_bytes_tma + tp.ring_offset);
+    const uint32_t bars = smem_u32(smem_bytes_tma + tp.bar_offset);
+    auto full_bar = [&](int st) { return bars + 8u * st; };
+    auto empty_bar = [&](int st) { return bars + 8u * (tp.stages + st); };
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int slices = (int)cluster.num_blocks();
+    const int slice = (int)cluster.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int k_warps = kTmaConsumerWarps / p.row_warps;
+    const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
+    const int L0 = slice * p.limbs_per_slice;
+    int nl = kl4 - L0;
+    nl = nl < 0 ? 0 : (nl > p.limbs_per_slice ? p.limbs_per_slice : nl);
+    const int chunks_cta = nl >> 2;
+    const int tok_stride = p.limbs_per_slice * 24 + 4;
+    const int plane_stride = p.ntok * tok_stride;
+    const int rows_per_cta = p.row_warps * 16;
+    const int64_t cta_row0 = (int64_t)blockIdx.x * rows_per_cta;
+
+    if (threadIdx.x == 0) {
+        for (int st = 0; st < tp.stages; ++st) { mbar_init(full_bar(st), 1); mbar_init(empty_bar(st), p.row_warps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // Several accumulator sets: consecutive MMAs of a chunk do not wait for one another.
+    constexpr int NACC = 4;
+    float acc[NACC][TOKB][4];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a)
+#pragma unroll
+        for (int b = 0; b < TOKB; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.0f;
+    int rw = 0, kw = 0;
+
+    if (warp == kTmaConsumerWarps) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int c = 0; c < chunks_cta && ok; ++c) {
+                const int st = c % tp.stages;
+                const uint32_t phase = (uint32_t)(c / tp.stages) & 1u;
+                ok = mbar_wait(empty_bar(st), phase ^ 1u);
+                if (!ok) break;
+                mbar_arrive_expect_tx(full_bar(st), (uint32_t)tp.stage_bytes);
+                tma_load_2d(ring + (uint32_t)st * tp.stage_bytes, &map_w, (L0 + 4 * c) * 16, (int)cta_row0, full_bar(st));
+            }
+            if (!ok) atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_PRODUCER);
+        }
+    } else {
+        // ---------------- consumers ----------------
+        rw = warp % p.row_warps;
+        kw = warp / p.row_warps;
+        stage_activations<XT, PLANES, CONSUMER_THREADS>(p, L0, nl, xs, tok_stride, plane_stride);
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");  // consumers only; the producer is already streaming
+
+        int tok_off[TOKB];
+#pragma unroll
+        for (int b = 0; b < TOKB; ++b) tok_off[b] = (8 * b + g < p.ntok ? 8 * b + g : 0) * tok_stride + t * 24;
+        const uint32_t lane_off = (uint32_t)((rw * 16 + g) * 64 + t * 16);
+        bool ok = true;
+        for (int c = kw; c < chunks_cta; c += k_warps) {
+            const int st = c % tp.stages;
+            const uint32_t phase = (uint32_t)(c / tp.stages) & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(st), phase));
+            if (!ok) break;
+            const uint8_t *tile = smem_bytes_tma + tp.ring_offset + st * tp.stage_bytes + lane_off;
+            const uint4 la = *reinterpret_cast<const uint4 *>(tile);
+            const uint4 lb = *reinterpret_cast<const uint4 *>(tile + 8 * 64);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(st));  // the limbs are in registers: the slot can be refilled
+            // activations of this chunk first (their latency hides behind the first decode), then,
+            // word by word: decode 4 + 4 trytes, issue the 3 MMAs that consume them.
+            uint4 xr[TOKB][PLANES][6];
+#pragma unroll
+            for (int b = 0; b < TOKB; ++b)
+#pragma unroll
+                for (int pl = 0; pl < PLANES; ++pl) {
+                    const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96);
+#pragma unroll
+                    for (int q = 0; q < 6; ++q) xr[b][pl][q] = xv[q];
+                }
+            const uint32_t aw[4] = {la.x, la.y, la.z, la.w}, bw[4] = {lb.x, lb.y, lb.z, lb.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                uint32_t oa[6], ob[6];
+                decode_word_pair(aw[w], bw[w], oa, ob);
+#pragma unroll
+                for (int b = 0; b < TOKB; ++b)
+#pragma unroll
+                    for (int pl = 0; pl < PLANES; ++pl) {
+                        // registers 6w .. 6w+5 of the limb <-> activation registers 6w .. 6w+5
+                        const uint32_t *xw = reinterpret_cast<const uint32_t *>(&xr[b][pl][0]) + 6 * w;
+                        mma_bf16_16816(acc[(3 * w) % NACC][b], oa[0], ob[0], oa[1], ob[1], xw[0], xw[1]);
+                        mma_bf16_16816(acc[(3 * w + 1) % NACC][b], oa[2], ob[2], oa[3], ob[3], xw[2], xw[3]);
+                        mma_bf16_16816(acc[(3 * w + 2) % NACC][b], oa[4], ob[4], oa[5], ob[5], xw[4], xw[5]);
+                    }
+            }
+        }
+        if (!ok && lane == 0) atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_CONSUMER);
+
+        float *pw = part + (size_t)kw * rows_per_cta * kTokPad;
+        const int lr = rw * 16;
+#pragma unroll
+        for (int b = 0; b < TOKB; ++b) {
+            float r[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[i] = (acc[0][b][i] + acc[1][b][i]) + (acc[2][b][i] + acc[3][b][i]);
+            *reinterpret_cast<float2 *>(pw + (lr + g) * kTokPad + 8 * b + 2 * t) = make_float2(r[0], r[1]);
+            *reinterpret_cast<float2 *>(pw + (lr + g + 8) * kTokPad + 8 * b + 2 * t) = make_float2(r[2], r[3]);
+        }
+    }
+    __syncthreads();
+
+    const int outs = rows_per_cta * kTokPad;
+    if (slices == 1) {
+        for (int idx = threadIdx.x; idx < outs; idx += kTmaThreads) {
+            float s = part[idx];
+            for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
+            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < outs; idx += kTmaThreads) {
+            float s = part[idx];
+            for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
+            part[idx] = s;
+        }
+        cluster.sync();
+        const int span = (rows_per_cta + slices - 1) / slices;
+        const int lo = slice * span;
+        const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
+        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += kTmaThreads) {
+            float s = 0.0f;
+            for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
+            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+        }
+        cluster.sync();
+    }
+}
+
+template <typename XT, typename CT, int TOKB>
+int launch_tma(const CUtensorMap &map, const GemvTmaParams &tp, int slices, size_t smem_bytes, cudaStream_t st) {
+    auto kern = gemv_trit_tma_kernel<XT, CT, TOKB>;
+    T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    const int rows_per_cta = tp.g.row_warps * 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((tp.g.M + rows_per_cta - 1) / rows_per_cta), (unsigned)slices, 1);
+    cfg.blockDim = dim3(kTmaThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)slices;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    T81_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, tp));
+    return T81B200_OK;
+}
+
+template <typename XT>
+int launch_tma_ct(const CUtensorMap &map, const GemvTmaParams &tp, int c_dtype, int slices, size_t smem_bytes, cudaStream_t st) {
+    const bool wide = tp.g.ntok > 8;
+    switch (c_dtype) {
+        case T81B200_F32:
+            return wide ? launch_tma<XT, float, 2>(map, tp, slices, smem_bytes, st) : launch_tma<XT, float, 1>(map, tp, slices, smem_bytes, st);
+        case T81B200_BF16:
+            return wide ? launch_tma<XT, __nv_bfloat16, 2>(map, tp, slices, smem_bytes, st) : launch_tma<XT, __nv_bfloat16, 1>(map, tp, slices, smem_bytes, st);
+        case T81B200_F16:
+            return wide ? launch_tma<XT, __half, 2>(map, tp, slices, smem_bytes, st) : launch_tma<XT, __half, 1>(map, tp, slices, smem_bytes, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
+}
+
 size_t gemv_smem_bytes(int planes, int ntok, int tokpad, int lps, int warps, int row_warps, int rg) {
     return (size_t)planes * ntok * (lps * 24 + 4) * 4 + (size_t)(warps / row_warps) * row_warps * 16 * rg * tokpad * 4;
 }
 
+}  // namespace
+
+// Shape choice and launch of the TMA-fed kernel.  Returns T81B200_EALIGN when no configuration
+// fits (the caller then uses the register-prefetch kernel).
+int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaStream_t st) {
+    GemvTmaParams tp;
+    tp.g = base;
+    const int ntok = base.ntok;
+    const int planes = x_dtype == T81B200_BF16 ? 1 : 2;
+    const int tokpad = ntok > 8 ? 16 : 8;
+    const int kl4 = (int)((base.kl + 3) & ~(int64_t)3);
+    const int sms = sm_count();
+    const double sm_bw = 6.5e12 / sms;
+    const double chunk_rate = 4 * 1.8e9 / 280.0;  // chunks per second one SM decodes (4 schedulers)
+    const size_t budget = 200 * 1024;
+    int best_rw = 0, best_s = 1, best_lps = 4, best_stages = 0;
+    double best_t = 1e30;
+    int forced_rw = 0, forced_s = 0;
+    if (const char *env = getenv("T81B200_GEMV_TMA_CFG")) sscanf(env, "%d,%d", &forced_rw, &forced_s);
+    for (int rwv = 1; rwv <= kTmaConsumerWarps; rwv *= 2)
+        for (int s = 1; s <= 8; s *= 2) {
+            if (forced_rw && (rwv != forced_rw || s != forced_s)) continue;
+            const int kwv = kTmaConsumerWarps / rwv;
+            int lps = (kl4 / 4 + s - 1) / s * 4;
+            if (lps < 4) lps = 4;
+            if (s > 1 && (int64_t)(s - 1) * lps >= kl4) continue;
+            const int chunks = lps / 4;
+            if (kwv > chunks) continue;
+            const int rows = 16 * rwv;
+            const size_t xs_bytes = ((size_t)planes * ntok * (lps * 24 + 4) * 4 + 127) & ~(size_t)127;
+            const size_t part_bytes = ((size_t)kwv * rows * tokpad * 4 + 127) & ~(size_t)127;
+            const size_t stage_bytes = (size_t)rows * 64;
+            if (xs_bytes + part_bytes + 1024 + 2 * stage_bytes * kwv > budget) continue;
+            int stages = (int)((budget - xs_bytes - part_bytes - 1024) / stage_bytes);
+            if (stages > kTmaMaxStages) stages = kTmaMaxStages;
+            if (stages > chunks) stages = chunks;
+            if (stages < 2 * kwv && stages < chunks) continue;
+            const int64_t row_tiles = (base.M + rows - 1) / rows;
+            const double ctas = (double)row_tiles * s;
+            const double waves = ceil(ctas / sms);
+            const double in_flight_bw = (double)stages * stage_bytes / 1.5e-6;
+            const double stream = (double)rows * lps * 16 / (sm_bw < in_flight_bw ? sm_bw : in_flight_bw);
+            const double work = (double)rwv * chunks * (1.0 + 0.25 * (planes * (tokpad / 8) - 1)) / chunk_rate;
+            const double staging = (double)planes * ntok * lps * 96 / 1.0e11;
+            const double fixed = 2.0e-6 + (s > 1 ? 1.0e-6 : 0.0);
+            const double t = waves * (fixed + staging * 0.5 + (stream > work ? stream : work));
+            if (t < best_t) { best_t = t; best_rw = rwv; best_s = s; best_lps = lps; best_stages = stages; }
+        }
+    if (!best_rw) return T81B200_EALIGN;
+    const int kwv = kTmaConsumerWarps / best_rw;
+    const int rows = 16 * best_rw;
+    tp.g.row_warps = best_rw;
+    tp.g.row_groups = 1;
+    tp.g.limbs_per_slice = best_lps;
+    tp.stages = best_stages;
+    tp.stage_bytes = rows * 64;
+    const size_t xs_bytes = ((size_t)planes * ntok * (best_lps * 24 + 4) * 4 + 127) & ~(size_t)127;
+    const size_t part_bytes = ((size_t)kwv * rows * tokpad * 4 + 127) & ~(size_t)127;
+    tp.ring_offset = (int)xs_bytes;
+    tp.part_offset = (int)(xs_bytes + (size_t)best_stages * tp.stage_bytes);
+    tp.bar_offset = (int)(tp.part_offset + part_bytes);
+    const size_t smem = (size_t)tp.bar_offset + 16 * (size_t)best_stages + 128;
+    CUtensorMap map;
+    if (int rc = make_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base.A, (uint64_t)base.kl * 16, (uint64_t)base.M,
+                             (uint64_t)base.kl * 16, 64, (uint32_t)rows, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+    switch (x_dtype) {
+        case T81B200_BF16: return launch_tma_ct<__nv_bfloat16>(map, tp, c_dtype, best_s, smem, st);
+        case T81B200_F32: return launch_tma_ct<float>(map, tp, c_dtype, best_s, smem, st);
+        case T81B200_F16: return launch_tma_ct<__half>(map, tp, c_dtype, best_s, smem, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
+}
+
+int gemv_trit_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemv_status, sizeof v) != cudaSuccess) return T81B200_ECUDA;
+    if (reset && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof zero) != cudaSuccess) return T81B200_ECUDA;
+    }
+    return v;
+}
+
+namespace {
 }  // namespace
 
 // Host entry used by the dispatcher in capi.cu.  NK layout, ntok in 1..16, A 16-byte aligned.
@@ -374,6 +673,14 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     const int planes = x_dtype == T81B200_BF16 ? 1 : 2;
     const int tokpad = ntok > 8 ? 16 : 8;
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
+
+    // Default: the TMA-fed kernel.  T81B200_GEMV_PATH=ldg selects the register-prefetch kernel (A/B runs).
+    const char *path = getenv("T81B200_GEMV_PATH");
+    if (!(path && path[0] == 'l')) {
+        p.row_warps = 1; p.row_groups = 1; p.limbs_per_slice = 4;
+        const int rc = gemv_trit_tma_launch(p, x_dtype, c_dtype, st);
+        if (rc != T81B200_EALIGN) return rc;
+    }
 
     // Pick the CTA shape with a small cost model.  A CTA has W warps arranged as RW row groups
     // (16 rows each) x W/RW slices of its contraction range; RG row groups are walked in

@@ -57,7 +57,7 @@ constexpr int kChunkGroups = 192;  // float4 groups per warp step: 768 weights =
 
 // One warp owns one row at a time; there is no block-wide barrier anywhere.
 template <typename T, bool ABSMEAN>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 2)
 quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_t ld, float thr,
                      uint8_t *__restrict__ packed, float *__restrict__ row_scale, bool vec) {
     __shared__ uint32_t digit_smem[kWarpsPerCta][kChunkGroups];
@@ -78,14 +78,16 @@ quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_
             double part[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) part[j] = 0.0;
-            for (int64_t g0 = lane; g0 < groups; g0 += 256) {
-                float v[8][4];
+            // batches of 8 groups per lane (4 KB per warp), the next batch in flight while this one is summed
+            auto load_batch = [&](int64_t g0, float (&v)[8][4]) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int64_t g = g0 + 32 * j;
                     if (g < groups) load_group<T>(row, 4 * g, cols, vec, v[j]);
                     else { v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0.0f; }
                 }
+            };
+            auto sum_batch = [&](int64_t g0, const float (&v)[8][4]) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int64_t g = g0 + 32 * j;
@@ -93,6 +95,18 @@ quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
                             if (4 * g + c < cols) part[j] += (double)fabsf(v[j][c]);
+                    }
+                }
+            };
+            {
+                float va[8][4], vb[8][4];
+                load_batch(lane, va);
+                for (int64_t g0 = lane; g0 < groups; g0 += 512) {
+                    if (g0 + 256 < groups) load_batch(g0 + 256, vb);
+                    sum_batch(g0, va);
+                    if (g0 + 256 < groups) {
+                        if (g0 + 512 < groups) load_batch(g0 + 512, va);
+                        sum_batch(g0 + 256, vb);
                     }
                 }
             }
@@ -113,14 +127,19 @@ quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_
         }
 
         uint32_t *out = reinterpret_cast<uint32_t *>(packed + r * kl * 16);
-        for (int64_t gbase = 0; gbase < kl * 12; gbase += kChunkGroups) {
-            float v[6][4];
+        auto load_chunk = [&](int64_t gbase, float (&v)[6][4]) {
 #pragma unroll
             for (int q = 0; q < 6; ++q) {
                 const int64_t g = gbase + lane + 32 * q;
                 if (g < groups) load_group<T>(row, 4 * g, cols, vec, v[q]);
                 else { v[q][0] = v[q][1] = v[q][2] = v[q][3] = 0.0f; }
             }
+        };
+        float v[6][4], vnext[6][4];
+        load_chunk(0, v);
+        for (int64_t gbase = 0; gbase < kl * 12; gbase += kChunkGroups) {
+            const bool more = gbase + kChunkGroups < kl * 12;
+            if (more) load_chunk(gbase + kChunkGroups, vnext);  // in flight while this step is packed
 #pragma unroll
             for (int q = 0; q < 6; ++q) {
                 const int64_t g = gbase + lane + 32 * q;
@@ -152,6 +171,12 @@ quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_
                 }
             }
             __syncwarp();  // digits[] is reused by the next step
+            if (more) {
+#pragma unroll
+                for (int q = 0; q < 6; ++q)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) v[q][c] = vnext[q][c];
+            }
         }
     }
 }
