@@ -19,14 +19,12 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// Reference rule: clamp to [-1,1], inclusive compares, NaN -> 0.  Returns t+1.
+// Reference rule (clamp to [-1,1], then c >= thr -> +1, c <= -thr -> -1, else 0), returned
+// as t+1.  With thr <= 1 the clamp cannot change either comparison, and NaN fails both, so
+// two compares on the raw value are equivalent.  The negative test is applied last: at
+// thr == 0 a zero becomes -1, like the reference's Python quantiser (t81/torch/__init__.py:44-50).
 __device__ __forceinline__ uint32_t quantize_digit(float v, float thr) {
-    const float c = fminf(fmaxf(v, -1.0f), 1.0f);  // NaN: fmaxf(NaN,-1) = -1; handled below
-    uint32_t d = 1u;
-    if (c >= thr) d = 2u;
-    if (c <= -thr) d = 0u;
-    if (v != v) d = 1u;  // std::clamp leaves NaN, and both compares are false
-    return d;
+    return v <= -thr ? 0u : (v >= thr ? 2u : 1u);
 }
 
 template <typename T> struct Group4 {
@@ -181,6 +179,105 @@ quantize_pack_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_
     }
 }
 
+// Row-in-shared-memory variant: a small CTA (128 threads) owns one row at a time, keeps it as
+// floats in shared memory between the absmean pass and the quantise pass (each weight is read
+// from global memory exactly once), and many such CTAs share an SM (about 20 KB each for a
+// 4096-column row), so the three block barriers per row overlap across CTAs.  The summation
+// order is the same fixed one: thread tau owns partials tau and tau+128.
+constexpr int kRowThreads = 128;
+
+template <typename T, bool ABSMEAN>
+__global__ void __launch_bounds__(kRowThreads, 8)
+quantize_pack_row_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, int64_t ld, float thr,
+                         uint8_t *__restrict__ packed, float *__restrict__ row_scale, bool vec) {
+    extern __shared__ __align__(16) uint8_t row_smem[];
+    const int64_t kl = (cols + 47) / 48;
+    const int64_t groups = (cols + 3) / 4;
+    const int64_t digit_words = kl * 12;
+    float4 *rowf = reinterpret_cast<float4 *>(row_smem);                         // groups float4
+    uint32_t *digits = reinterpret_cast<uint32_t *>(row_smem + groups * 16);     // digit_words words
+    __shared__ double group_sum[8];
+    __shared__ float inv_shared;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T *row = w + r * ld;
+        double part[2] = {0.0, 0.0};
+        // m-th group of this thread: g = tid + 128 m; it belongs to partial g % 256 = tid + 128 (m % 2)
+        for (int64_t g0 = tid; g0 < groups; g0 += 8 * kRowThreads) {
+            float v[8][4];  // eight loads in flight per thread before any is used
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int64_t g = g0 + kRowThreads * j;
+                if (g < groups) load_group<T>(row, 4 * g, cols, vec, v[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int64_t g = g0 + kRowThreads * j;
+                if (g < groups) {
+                    rowf[g] = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+                    if constexpr (ABSMEAN) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (4 * g + c < cols) part[j & 1] += (double)fabsf(v[j][c]);
+                    }
+                }
+            }
+        }
+        float inv = 1.0f;
+        if constexpr (ABSMEAN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) part[j] += __shfl_down_sync(0xffffffffu, part[j], off);
+                if (lane == 0) group_sum[warp + 4 * j] = part[j];  // partials 32*(warp+4j) .. +31
+            }
+            __syncthreads();
+            if (tid == 0) {
+                double g8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g8[j] = group_sum[j];
+#pragma unroll
+                for (int off = 4; off >= 1; off >>= 1)
+#pragma unroll
+                    for (int j = 0; j < off; ++j) g8[j] += g8[j + off];
+                const float sr = (float)(g8[0] / (double)cols);
+                inv_shared = sr > 0.0f ? __fdiv_rn(1.0f, sr) : 0.0f;
+                row_scale[r] = sr;
+            }
+            __syncthreads();
+            inv = inv_shared;
+        }
+        // digits: each thread re-reads the groups it wrote itself (no barrier needed for rowf)
+        for (int64_t g = tid; g < digit_words; g += kRowThreads) {
+            uint32_t word = 0x01010101u;
+            if (g < groups) {
+                const float4 f = rowf[g];
+                const float v[4] = {f.x, f.y, f.z, f.w};
+                word = 0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float x = ABSMEAN ? __fmul_rn(v[c], inv) : v[c];
+                    const uint32_t d = 4 * g + c < cols ? quantize_digit(x, thr) : 1u;
+                    word |= d << (8 * c);
+                }
+            }
+            digits[g] = word;
+        }
+        __syncthreads();
+        uint32_t *out = reinterpret_cast<uint32_t *>(packed + r * kl * 16);
+        for (int64_t q = tid; q < kl * 4; q += kRowThreads) {
+            const uint32_t a = digits[3 * q], b = digits[3 * q + 1], c = digits[3 * q + 2];
+            const uint32_t y0 = (a & 0xff) + 3u * ((a >> 8) & 0xff) + 9u * ((a >> 16) & 0xff);
+            const uint32_t y1 = (a >> 24) + 3u * (b & 0xff) + 9u * ((b >> 8) & 0xff);
+            const uint32_t y2 = ((b >> 16) & 0xff) + 3u * (b >> 24) + 9u * (c & 0xff);
+            const uint32_t y3 = ((c >> 8) & 0xff) + 3u * ((c >> 16) & 0xff) + 9u * (c >> 24);
+            out[q] = y0 | (y1 << 8) | (y2 << 16) | (y3 << 24);
+        }
+        __syncthreads();  // rowf / digits are reused by the next row
+    }
+}
+
 __global__ void quantize_trits_kernel(const float *__restrict__ src, int64_t n, float thr,
                                       int8_t *__restrict__ dst) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -211,6 +308,19 @@ template <typename T>
 int launch_quantize_pack(const void *w, int64_t rows, int64_t cols, int64_t ld, float thr, int rule,
                          uint8_t *packed, float *row_scale, cudaStream_t st) {
     const bool vec = (reinterpret_cast<uintptr_t>(w) % (4 * sizeof(T)) == 0) && (ld % 4 == 0);
+    // rows that fit shared memory several times per SM: the row-in-shared-memory kernel
+    const int64_t kl = (cols + 47) / 48;
+    const size_t row_bytes = (size_t)((cols + 3) / 4) * 16 + (size_t)kl * 48;
+    if (row_bytes <= 64 * 1024) {
+        auto rk = rule == T81B200_RULE_ABSMEAN ? quantize_pack_row_kernel<T, true> : quantize_pack_row_kernel<T, false>;
+        if (row_bytes > 48 * 1024)
+            T81_CUDA_TRY(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes));
+        const int64_t cap = (int64_t)sm_count() * 16;
+        const int g = (int)(rows < cap ? rows : cap);
+        rk<<<g, kRowThreads, row_bytes, st>>>(static_cast<const T *>(w), rows, cols, ld, thr, packed, row_scale, vec);
+        T81_LAUNCH_CHECK("quantize_pack_row_kernel");
+        return T81B200_OK;
+    }
     const int64_t ctas = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
     const int grid = (int)(ctas < (int64_t)sm_count() * 8 ? ctas : (int64_t)sm_count() * 8);
     auto kern = rule == T81B200_RULE_ABSMEAN ? quantize_pack_kernel<T, true> : quantize_pack_kernel<T, false>;
