@@ -50,7 +50,7 @@ class ShardedLinear(nn.Module):
 
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, threshold: float = 0.45,
                  rule: str = "fixed", group=None, rank: Optional[int] = None, world_size: Optional[int] = None,
-                 matmul=None, quantize=None):
+                 shard_min_tokens: int = 0, matmul=None, quantize=None):
         super().__init__()
         if weight.ndim != 2:
             raise ValueError("t81.trit tensors currently only support 2D matrices")
@@ -62,11 +62,26 @@ class ShardedLinear(nn.Module):
         self.rows = (lo, hi)
         self.ternary_threshold = threshold
         self.ternary_rule = rule
+        # Calls with fewer tokens than this run unsharded on every rank: an all-gather costs tens
+        # of microseconds, a decode-sized matmul a few.  Needs the whole packed matrix on every
+        # rank (2.67 bits per weight); the shard is then a view of it, not a second copy.
+        self.shard_min_tokens = shard_min_tokens
+        self._full_matmul = None
+        self._full_bias = None if bias is None or shard_min_tokens <= 0 else bias.detach().clone()
         # `quantize` / `matmul` are injection points for host-side tests of the sharding
         # logic; the defaults are the device kernels.
         if quantize is None:
             from .. import torch as t81_torch
-            self.ternary_weight = t81_torch.TernaryTensor.from_float(weight[lo:hi].detach(), threshold=threshold, rule=rule)
+            if shard_min_tokens > 0:
+                full = t81_torch.TernaryTensor.from_float(weight.detach(), threshold=threshold, rule=rule)
+                self.full_weight = full
+                scale = None if full.row_scale is None else full.row_scale[lo:hi]
+                self.ternary_weight = t81_torch.TernaryTensor(
+                    full.packed[lo:hi], (hi - lo, self.in_features), k_actual=self.in_features, k_limbs=full.packed.shape[1],
+                    threshold=threshold, row_scale=scale, rule=rule)
+                self._full_matmul = lambda x, b: full.matmul_input(x, bias=b)
+            else:
+                self.ternary_weight = t81_torch.TernaryTensor.from_float(weight[lo:hi].detach(), threshold=threshold, rule=rule)
             self._matmul = lambda x, b: self.ternary_weight.matmul_input(x, bias=b)
         else:
             self.ternary_weight = quantize(weight[lo:hi].detach(), threshold, rule)
@@ -91,6 +106,11 @@ class ShardedLinear(nn.Module):
         if x.ndim == 3:
             b, s, f = x.shape
             return self.forward(x.reshape(b * s, f)).reshape(b, s, -1)
+        if self._full_matmul is not None and x.shape[0] < self.shard_min_tokens:
+            bias = self._full_bias
+            if bias is not None and bias.device != x.device:
+                bias = self._full_bias = bias.to(x.device)
+            return self._full_matmul(x, bias)
         local = self.forward_local(x)
         if self.world_size == 1:
             return local
