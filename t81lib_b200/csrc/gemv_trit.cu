@@ -71,9 +71,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Stage the activations of limbs [L0, L0+nl) for `ntok` tokens into shared memory in
 // decode_limb register order.  Plane 0 holds bf16(x); plane 1 (PLANES == 2) holds
 // bf16(x - plane0), so that plane0 + plane1 carries 16 mantissa bits of an fp32 input.
-template <typename XT, int PLANES, int THREADS>
+template <typename XT, int PLANES>
 __device__ __forceinline__ void stage_activations(const GemvParams &p, int L0, int nl, uint32_t *xs,
-                                                  int tok_stride, int plane_stride) {
+                                                  int tok_stride, int plane_stride, int THREADS) {
     const XT *X = static_cast<const XT *>(p.X);
     const bool vec_ok = sizeof(XT) == 2 && (reinterpret_cast<uintptr_t>(X) % 16 == 0) && (p.ldx % 8 == 0);
     for (int item = threadIdx.x; item < p.ntok * nl; item += THREADS) {
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(WARPS * 32, VAR == 1 ? (WARPS == 8 ? 4 : 2) : 
     // before the activations are staged.
     set_rows(0);
     if (c_begin < c_end) prefetch_head();
-    stage_activations<XT, PLANES, THREADS>(p, L0, nl, xs, tok_stride, plane_stride);
+    stage_activations<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride, THREADS);
     __syncthreads();
 
     // lanes whose token does not exist read token 0; their results are never stored
@@ -369,8 +369,8 @@ int launch_ct(const GemvParams &p, int c_dtype, int warps, int slices, size_t sm
 // and decode / multiply exactly as above.
 // ---------------------------------------------------------------------------------------------
 
-constexpr int kTmaConsumerWarps = 16;
-constexpr int kTmaThreads = (kTmaConsumerWarps + 1) * 32;
+constexpr int kTmaMaxConsumerWarps = 16;
+constexpr int kTmaMaxThreads = (kTmaMaxConsumerWarps + 1) * 32;
 constexpr int kTmaMaxStages = 48;
 
 enum { GEMV_STATUS_OK = 0, GEMV_STATUS_TIMEOUT_PRODUCER = 5, GEMV_STATUS_TIMEOUT_CONSUMER = 6 };
@@ -378,6 +378,7 @@ __device__ int g_gemv_status = 0;
 
 struct GemvTmaParams {
     GemvParams g;
+    int consumer_warps;  // RW * KW <= 16; one more warp produces
     int stages;        // ring depth
     int stage_bytes;   // 16*RW*64
     int ring_offset;   // bytes from the start of dynamic shared memory (128-byte aligned)
@@ -386,11 +387,12 @@ struct GemvTmaParams {
 };
 
 template <typename XT, typename CT, int TOKB>
-__global__ void __launch_bounds__(kTmaThreads, 1)
+__global__ void __launch_bounds__(kTmaMaxThreads, 1)
 gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaParams tp) {
     constexpr int PLANES = Planes<XT>::value;
     constexpr int kTokPad = 8 * TOKB;
-    constexpr int CONSUMER_THREADS = kTmaConsumerWarps * 32;
+    const int consumer_threads = tp.consumer_warps * 32;
+    const int all_threads = consumer_threads + 32;
     const GemvParams &p = tp.g;
     extern __shared__ __align__(128) uint8_t smem_bytes_tma[];
     uint32_t *xs = reinterpret_cast<uint32_t *>(smem_bytes_tma);
@@ -405,7 +407,7 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
     const int slice = (int)cluster.block_rank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int k_warps = kTmaConsumerWarps / p.row_warps;
+    const int k_warps = tp.consumer_warps / p.row_warps;
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
     const int L0 = slice * p.limbs_per_slice;
     int nl = kl4 - L0;
@@ -421,6 +423,10 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // Programmatic dependent launch: the next kernel in the stream may start now (it will wait
+    // for this one where it needs to).  The weight stream below depends on no earlier kernel,
+    // so it starts before the wait; activations, C and every store come after it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Several accumulator sets: consecutive MMAs of a chunk do not wait for one another.
     constexpr int NACC = 4;
@@ -431,7 +437,7 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
         for (int b = 0; b < TOKB; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.0f;
     int rw = 0, kw = 0;
 
-    if (warp == kTmaConsumerWarps) {
+    if (warp == tp.consumer_warps) {
         // ---------------- producer ----------------
         if (lane == 0) {
             bool ok = true;
@@ -445,12 +451,14 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
             }
             if (!ok) atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_PRODUCER);
         }
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // before this warp's share of the output stores
     } else {
         // ---------------- consumers ----------------
         rw = warp % p.row_warps;
         kw = warp / p.row_warps;
-        stage_activations<XT, PLANES, CONSUMER_THREADS>(p, L0, nl, xs, tok_stride, plane_stride);
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");  // consumers only; the producer is already streaming
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
+        stage_activations<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride, consumer_threads);
+        asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // consumers only; the producer is already streaming
 
         int tok_off[TOKB];
 #pragma unroll
@@ -512,13 +520,13 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
 
     const int outs = rows_per_cta * kTokPad;
     if (slices == 1) {
-        for (int idx = threadIdx.x; idx < outs; idx += kTmaThreads) {
+        for (int idx = threadIdx.x; idx < outs; idx += all_threads) {
             float s = part[idx];
             for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
             store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
         }
     } else {
-        for (int idx = threadIdx.x; idx < outs; idx += kTmaThreads) {
+        for (int idx = threadIdx.x; idx < outs; idx += all_threads) {
             float s = part[idx];
             for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
             part[idx] = s;
@@ -527,7 +535,7 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
         const int span = (rows_per_cta + slices - 1) / slices;
         const int lo = slice * span;
         const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
-        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += kTmaThreads) {
+        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += all_threads) {
             float s = 0.0f;
             for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
             store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
@@ -543,16 +551,19 @@ int launch_tma(const CUtensorMap &map, const GemvTmaParams &tp, int slices, size
     const int rows_per_cta = tp.g.row_warps * 16;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((tp.g.M + rows_per_cta - 1) / rows_per_cta), (unsigned)slices, 1);
-    cfg.blockDim = dim3(kTmaThreads, 1, 1);
+    cfg.blockDim = dim3((tp.consumer_warps + 1) * 32, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = (unsigned)slices;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static const bool pdl = !(getenv("T81B200_NO_PDL"));
+    cfg.numAttrs = pdl ? 2 : 1;
     T81_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, tp));
     return T81B200_OK;
 }
@@ -587,45 +598,51 @@ int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaS
     const int tokpad = ntok > 8 ? 16 : 8;
     const int kl4 = (int)((base.kl + 3) & ~(int64_t)3);
     const int sms = sm_count();
-    const double sm_bw = 6.5e12 / sms;
-    const double chunk_rate = 4 * 1.8e9 / 280.0;  // chunks per second one SM decodes (4 schedulers)
     const size_t budget = 200 * 1024;
     int best_rw = 0, best_s = 1, best_lps = 4, best_stages = 0;
     double best_t = 1e30;
-    int forced_rw = 0, forced_s = 0;
-    if (const char *env = getenv("T81B200_GEMV_TMA_CFG")) sscanf(env, "%d,%d", &forced_rw, &forced_s);
-    for (int rwv = 1; rwv <= kTmaConsumerWarps; rwv *= 2)
-        for (int s = 1; s <= 8; s *= 2) {
-            if (forced_rw && (rwv != forced_rw || s != forced_s)) continue;
-            const int kwv = kTmaConsumerWarps / rwv;
-            int lps = (kl4 / 4 + s - 1) / s * 4;
-            if (lps < 4) lps = 4;
-            if (s > 1 && (int64_t)(s - 1) * lps >= kl4) continue;
-            const int chunks = lps / 4;
-            if (kwv > chunks) continue;
-            const int rows = 16 * rwv;
-            const size_t xs_bytes = ((size_t)planes * ntok * (lps * 24 + 4) * 4 + 127) & ~(size_t)127;
-            const size_t part_bytes = ((size_t)kwv * rows * tokpad * 4 + 127) & ~(size_t)127;
-            const size_t stage_bytes = (size_t)rows * 64;
-            if (xs_bytes + part_bytes + 1024 + 2 * stage_bytes * kwv > budget) continue;
-            int stages = (int)((budget - xs_bytes - part_bytes - 1024) / stage_bytes);
-            if (stages > kTmaMaxStages) stages = kTmaMaxStages;
-            if (stages > chunks) stages = chunks;
-            if (stages < 2 * kwv && stages < chunks) continue;
-            const int64_t row_tiles = (base.M + rows - 1) / rows;
-            const double ctas = (double)row_tiles * s;
-            const double waves = ceil(ctas / sms);
-            const double in_flight_bw = (double)stages * stage_bytes / 1.5e-6;
-            const double stream = (double)rows * lps * 16 / (sm_bw < in_flight_bw ? sm_bw : in_flight_bw);
-            const double work = (double)rwv * chunks * (1.0 + 0.25 * (planes * (tokpad / 8) - 1)) / chunk_rate;
-            const double staging = (double)planes * ntok * lps * 96 / 1.0e11;
-            const double fixed = 2.0e-6 + (s > 1 ? 1.0e-6 : 0.0);
-            const double t = waves * (fixed + staging * 0.5 + (stream > work ? stream : work));
-            if (t < best_t) { best_t = t; best_rw = rwv; best_s = s; best_lps = lps; best_stages = stages; }
-        }
+    int forced_rw = 0, forced_s = 0, forced_kw = 0;  // T81B200_GEMV_TMA_CFG="row_warps,slices[,k_warps]" (sweeps)
+    if (const char *env = getenv("T81B200_GEMV_TMA_CFG")) sscanf(env, "%d,%d,%d", &forced_rw, &forced_s, &forced_kw);
+    int best_kw = 1;
+    for (int rwv = 1; rwv <= kTmaMaxConsumerWarps; ++rwv)
+        for (int kwv = 1; rwv * kwv <= kTmaMaxConsumerWarps; ++kwv)
+            for (int s = 1; s <= 4; s *= 2) {  // clusters of 8 were slower in every measured case
+                if (forced_rw && (rwv != forced_rw || s != forced_s || (forced_kw && kwv != forced_kw))) continue;
+                if (!forced_rw && kwv != 2 && kwv != 4) continue;  // 1 couples all warps to one slot, 8 starves each slice
+                int lps = (kl4 / 4 + s - 1) / s * 4;
+                if (lps < 4) lps = 4;
+                if (s > 1 && (int64_t)(s - 1) * lps >= kl4) continue;
+                const int chunks = lps / 4;
+                if (kwv > chunks) continue;
+                const int rows = 16 * rwv;
+                const size_t xs_bytes = ((size_t)planes * ntok * (lps * 24 + 4) * 4 + 127) & ~(size_t)127;
+                const size_t part_bytes = ((size_t)kwv * rows * tokpad * 4 + 127) & ~(size_t)127;
+                const size_t stage_bytes = (size_t)rows * 64;
+                if (xs_bytes + part_bytes + 1024 + 2 * stage_bytes * kwv > budget) continue;
+                int stages = (int)((budget - xs_bytes - part_bytes - 1024) / stage_bytes);
+                if (stages > kTmaMaxStages) stages = kTmaMaxStages;
+                if (stages > chunks) stages = chunks;
+                if (stages < 2 * kwv && stages < chunks) continue;
+                // Cost model fitted to a sweep over the Llama / Phi shapes (zero regret on it): a warp needs
+                // about 1400 cycles per chunk whatever shares its scheduler, up to four warps per scheduler;
+                // staging the activations runs at ~80 GB/s per CTA; a launch costs ~2.5 us, a cluster 0.7 more.
+                const int64_t row_tiles = (base.M + rows - 1) / rows;
+                // clusters must fit inside a GPC: fewer CTAs are co-resident than there are SMs
+                // (148 CTAs in clusters of 4 measured twice as slow as 128)
+                const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : sms - 20);
+                const double waves = ceil((double)row_tiles * s / wave_ctas);
+                const double warps_per_sched = ceil(rwv * kwv / 4.0);
+                const double chunks_per_warp = ceil((double)chunks / kwv);
+                const double work = chunks_per_warp * 1400.0 * (warps_per_sched > 4.0 ? warps_per_sched / 4.0 : 1.0) *
+                                    (1.0 + 0.25 * (planes * (tokpad / 8) - 1)) / 1.9e9;
+                const double staging = (double)planes * ntok * lps * 96 / 8.0e10;
+                const double t = waves * (2.5e-6 + (s > 1 ? 0.7e-6 : 0.0) + staging + work);
+                if (t < best_t) { best_t = t; best_rw = rwv; best_kw = kwv; best_s = s; best_lps = lps; best_stages = stages; }
+            }
     if (!best_rw) return T81B200_EALIGN;
-    const int kwv = kTmaConsumerWarps / best_rw;
+    const int kwv = best_kw;
     const int rows = 16 * best_rw;
+    tp.consumer_warps = best_rw * best_kw;
     tp.g.row_warps = best_rw;
     tp.g.row_groups = 1;
     tp.g.limbs_per_slice = best_lps;
