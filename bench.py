@@ -419,19 +419,41 @@ def e2e_public_api(torch, dev, Linear, layers, args):
     out_p = torch.empty(ptok, HIDDEN, dtype=torch.bfloat16).pin_memory()
     out_d = torch.empty(dtok, HIDDEN, dtype=torch.bfloat16).pin_memory()
 
-    def forward(host, out_host):
-        x = {w: host[w].to(dev, non_blocking=True) for w in host}
+    def run_modules(x):
         y = None
         with torch.no_grad():
             for row in mods:
                 for (name, out_f, in_f), m in zip(LINEARS, row):
                     y = m(x[in_f])
-        out_host.copy_(y, non_blocking=True)
+        return y
+
+    def forward(host, out_host):
+        x = {w: host[w].to(dev, non_blocking=True) for w in host}
+        out_host.copy_(run_modules(x), non_blocking=True)
+
+    # The decode pass (224 module calls on 8 tokens) is captured once in a CUDA graph, the way an
+    # inference server drives nn.Modules: every step still copies its inputs in from pinned host
+    # memory and its result back out.
+    x_static = {w: torch.zeros(dtok, w, dtype=torch.bfloat16, device=dev) for w in (HIDDEN, FFN)}
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        run_modules(x_static)
+        torch.cuda.synchronize()
+        dgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(dgraph, stream=stream):
+            y_static = run_modules(x_static)
+    torch.cuda.synchronize()
+
+    def decode_forward():
+        for w in x_static:
+            x_static[w].copy_(host_d[w], non_blocking=True)
+        dgraph.replay()
+        out_d.copy_(y_static, non_blocking=True)
 
     def job():
         forward(host_p, out_p)
         for _ in range(DECODE):
-            forward(host_d, out_d)
+            decode_forward()
 
     steps = max(1, min(args.steps, 3))
     job()
@@ -446,7 +468,7 @@ def e2e_public_api(torch, dev, Linear, layers, args):
     h2d = 2 * (ptok + DECODE * dtok) * (HIDDEN + FFN)
     d2h = 2 * (ptok + DECODE * dtok) * HIDDEN
     return {"value": BATCH * (PREFILL + DECODE) / sec, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": d2h, "steps": steps, "api": "t81lib_b200.nn.Linear.forward (eager, no CUDA graph)"}
+            "d2h_bytes_per_step": d2h, "steps": steps, "api": "t81lib_b200.nn.Linear.forward (prefill eager; decode pass replayed from a torch.cuda.CUDAGraph)"}
 
 
 def quantize_pack_line(torch, dev, ops, pk):

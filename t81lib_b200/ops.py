@@ -161,12 +161,23 @@ def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: 
     b_code, c_code = _dtype_code(B, "B"), _dtype_code(C, "C")
     ldb = B.stride(0) if B.shape[0] > 1 else max(B.shape[1], 1)
     ldc = C.stride(0) if C.shape[0] > 1 else max(C.shape[1], 1)
-    rs = None if row_scale is None else row_scale.to(device=B.device, dtype=torch.float32).contiguous()
-    bs = None if bias is None else bias.to(device=B.device, dtype=torch.float32).contiguous()
-    with torch.cuda.device(B.device):
-        need = _capi.lib.t81b200_gemm_trit_workspace_bytes(b_code, code, c_code, M, N, K)
-        ws = _workspace(B.device, need)
+    dev = B.device
+    rs = row_scale
+    if rs is not None and (rs.dtype != torch.float32 or rs.device != dev or not rs.is_contiguous()):
+        rs = rs.to(device=dev, dtype=torch.float32).contiguous()
+    bs = bias
+    if bs is not None and (bs.dtype != torch.float32 or bs.device != dev or not bs.is_contiguous()):
+        bs = bs.detach().to(device=dev, dtype=torch.float32).contiguous()
+    direct = b_code == _capi.BF16 and code == _capi.LAYOUT_NK  # no scratch needed
+    if direct and dev.index == torch.cuda.current_device():
+        _capi.check(_capi.lib.t81b200_gemm_trit(
+            packed.data_ptr(), _ptr(rs), B.data_ptr(), b_code, code, ldb, _ptr(bs), C.data_ptr(), c_code, ldc,
+            M, N, K, float(alpha), float(beta), None, 0, torch.cuda.current_stream(dev).cuda_stream))
+        return C
+    with torch.cuda.device(dev):
+        need = 0 if direct else _capi.lib.t81b200_gemm_trit_workspace_bytes(b_code, code, c_code, M, N, K)
+        ws = _workspace(dev, need)
         _capi.check(_capi.lib.t81b200_gemm_trit(
             _ptr(packed), _ptr(rs), _ptr(B), b_code, code, ldb, _ptr(bs), _ptr(C), c_code, ldc,
-            M, N, K, float(alpha), float(beta), _ptr(ws), 0 if ws is None else ws.numel(), _stream(B.device)))
+            M, N, K, float(alpha), float(beta), _ptr(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return C

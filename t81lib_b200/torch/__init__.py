@@ -169,6 +169,13 @@ class TernaryTensor(torch.Tensor):
         t81/torch/__init__.py:241-246 with the bias keyword of t81/nn/linear.py:62."""
         if input.ndim != 2:
             raise ValueError("t81.trit linear helpers expect 2D activations")
+        needs_grad = torch.is_grad_enabled() and (input.requires_grad or (bias is not None and bias.requires_grad))
+        if not needs_grad and input.is_cuda and input.device == self._base_device:
+            # inference fast path: no autograd node, no device shuffling — one kernel call
+            if input.shape[1] != self._k_actual:
+                raise ValueError("rhs dimension does not match ternary weight width")
+            return ops.gemm_trit(self._packed, input, M=self._rows, K=self._k_actual, layout="nk",
+                                 row_scale=self._row_scale, bias=bias, out_dtype=out_dtype)
         return _TernaryLinearFunction.apply(self, input, bias, out_dtype)
 
     @classmethod
