@@ -184,6 +184,33 @@ T81B200_API int t81b200_gemm_trit_static(const uint8_t *A, const float *row_scal
  * asynchronous pipeline). */
 T81B200_API int t81b200_kernel_status(int reset);
 
+/* TRIT-mode matmul of a column-sharded Linear: as t81b200_gemm_trit, and every element
+ * written to C is also written at the same offset of peer_C[0..n_peers), the results of
+ * the other GPUs of the node, mapped into this process (CUDA IPC / peer access); same
+ * dtype and ldc as C.  Each rank passes the column block it owns as C (a pointer into
+ * its full-width result), so that when all ranks' calls have completed every result is
+ * whole: an all-gather without a second pass over the data.  The tensor-core kernel
+ * stores to the peers from its epilogue (plain stores over NVLink while the next tile
+ * is multiplied); the other kernels are followed by t81b200_copy_columns per peer.
+ * beta applies to the local C only.  The caller orders "all ranks have finished" itself
+ * (a barrier or flag exchange after the call).  No counterpart in the reference (it has
+ * no multi-GPU path). */
+#define T81B200_MAX_PEERS 7
+T81B200_API int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale, const void *B, int b_dtype,
+                            int layout, int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc,
+                            int64_t M, int64_t N, int64_t K, float alpha, float beta, void *workspace,
+                            size_t workspace_bytes, int n_peers, void *const *peer_C, void *stream);
+
+/* Column-block copy for the column-sharded Linear: copies `rows` rows of `width_bytes`
+ * bytes from src (row pitch src_pitch bytes) to dst (row pitch dst_pitch bytes) on the
+ * copy engines, stream-ordered.  dst may be memory of another GPU of the same node
+ * that the caller has mapped into this process (CUDA IPC / peer access): a rank pushes
+ * the output features it computed into every peer's full-width result this way, so no
+ * SM is taken from the matmul that runs meanwhile.  No counterpart in the reference
+ * (it has no multi-GPU path). */
+T81B200_API int t81b200_copy_columns(void *dst, int64_t dst_pitch, const void *src, int64_t src_pitch,
+                         int64_t width_bytes, int64_t rows, void *stream);
+
 T81B200_API size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int c_dtype, int64_t M,
                                          int64_t N, int64_t K);
 

@@ -79,10 +79,11 @@ size_t gemm_trit_tc_workspace(int b_dtype, int layout, int c_dtype, int64_t M, i
 int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                         int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int64_t N,
                         int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes,
-                        cudaStream_t st);
+                        cudaStream_t st, int n_peers, void *const *peer_C);
 
 int gemm_trit_tc_status(int reset);
 int gemv_trit_status(int reset);
+int gemv_trit_umma_status(int reset);
 
 }  // namespace t81b200
 
@@ -92,7 +93,21 @@ extern "C" int t81b200_kernel_status(int reset) {
     if (int rc = check_device()) return rc;
     const int tc = gemm_trit_tc_status(reset);
     const int gv = gemv_trit_status(reset);
-    return tc != 0 ? tc : gv;
+    const int um = gemv_trit_umma_status(reset);
+    return tc != 0 ? tc : (gv != 0 ? gv : um);
+}
+
+extern "C" int t81b200_copy_columns(void *dst, int64_t dst_pitch, const void *src, int64_t src_pitch,
+                                    int64_t width_bytes, int64_t rows, void *stream) {
+    if (int rc = check_device()) return rc;
+    if (width_bytes < 0 || rows < 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
+        return fail(T81B200_EINVAL, "copy_columns: pitches (%lld, %lld) must cover the row width %lld",
+                    (long long)dst_pitch, (long long)src_pitch, (long long)width_bytes);
+    if (width_bytes == 0 || rows == 0) return T81B200_OK;
+    if (!dst || !src) return fail(T81B200_EINVAL, "copy_columns: null pointer");
+    T81_CUDA_TRY(cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width_bytes, (size_t)rows,
+                                   cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return T81B200_OK;
 }
 
 extern "C" const char *t81b200_last_error(void) { return g_error; }
@@ -110,10 +125,62 @@ extern "C" size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int
     return gemm_trit_tc_workspace(b_dtype, layout, c_dtype, M, N, K);
 }
 
+static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
+                           int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
+                           int64_t N, int64_t K, float alpha, float beta, void *workspace,
+                           size_t workspace_bytes, void *stream, int n_peers, void *const *peer_C, bool *peers_done);
+
 extern "C" int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                                  int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                                  int64_t N, int64_t K, float alpha, float beta, void *workspace,
                                  size_t workspace_bytes, void *stream) {
+    bool unused = false;
+    return gemm_trit_local(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, workspace,
+                           workspace_bytes, stream, 0, nullptr, &unused);
+}
+
+extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
+                                       int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
+                                       int64_t N, int64_t K, float alpha, float beta, void *workspace,
+                                       size_t workspace_bytes, int n_peers, void *const *peer_C, void *stream) {
+    if (n_peers < 0 || n_peers > T81B200_MAX_PEERS)
+        return fail(T81B200_ELIMIT, "gemm_trit_peers: %d peers, at most %d are supported", n_peers, T81B200_MAX_PEERS);
+    if (int rc = check_device()) return rc;
+    int cur = 0;
+    T81_CUDA_TRY(cudaGetDevice(&cur));
+    for (int i = 0; i < n_peers; ++i) {
+        if (!peer_C || !peer_C[i]) return fail(T81B200_EINVAL, "gemm_trit_peers: null peer pointer");
+        // the kernels store to these addresses: they must be device memory this GPU can reach
+        cudaPointerAttributes attr;
+        T81_CUDA_TRY(cudaPointerGetAttributes(&attr, peer_C[i]));
+        if (attr.type != cudaMemoryTypeDevice)
+            return fail(T81B200_EINVAL, "gemm_trit_peers: peer result %d is not device memory", i);
+        if (attr.device != cur) {
+            int can = 0;
+            T81_CUDA_TRY(cudaDeviceCanAccessPeer(&can, cur, attr.device));
+            if (!can) return fail(T81B200_EINVAL, "gemm_trit_peers: GPU %d cannot reach GPU %d", cur, attr.device);
+            const cudaError_t e = cudaDeviceEnablePeerAccess(attr.device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+            else if (e != cudaSuccess) return fail(T81B200_ECUDA, "gemm_trit_peers: enabling peer access to GPU %d: %s", attr.device, cudaGetErrorString(e));
+        }
+    }
+    bool peers_done = false;
+    if (int rc = gemm_trit_local(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta,
+                                 workspace, workspace_bytes, stream, n_peers, peer_C, &peers_done))
+        return rc;
+    if (peers_done || n_peers == 0 || M == 0 || N == 0) return T81B200_OK;
+    // a kernel without peer stores produced C: push the block with the copy engines instead
+    const int64_t esz = (int64_t)dtype_size(c_dtype);
+    const int64_t rows = layout == T81B200_LAYOUT_NK ? N : M, width = (layout == T81B200_LAYOUT_NK ? M : N) * esz;
+    for (int i = 0; i < n_peers; ++i)
+        if (int rc = t81b200_copy_columns(peer_C[i], ldc * esz, C, ldc * esz, width, rows, stream)) return rc;
+    return T81B200_OK;
+}
+
+static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
+                           int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
+                           int64_t N, int64_t K, float alpha, float beta, void *workspace,
+                           size_t workspace_bytes, void *stream, int n_peers, void *const *peer_C, bool *peers_done) {
     if (M < 0 || N < 0 || K < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
     if (!valid_dtype(b_dtype) || !valid_dtype(c_dtype)) return fail(T81B200_EINVAL, "gemm_trit: unknown dtype");
     if (layout != T81B200_LAYOUT_KN && layout != T81B200_LAYOUT_NK)
@@ -139,8 +206,11 @@ extern "C" int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const
         if (need > 0 && (!workspace || workspace_bytes < need))
             return fail(T81B200_EWORKSPACE, "gemm_trit: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
         const int rc = gemm_trit_tc_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K,
-                                           alpha, beta, workspace, workspace_bytes, st);
-        if (rc != T81B200_EALIGN) return rc;  // unaligned activations: the general kernel takes them
+                                           alpha, beta, workspace, workspace_bytes, st, n_peers, peer_C);
+        if (rc != T81B200_EALIGN) {  // unaligned activations: the general kernel takes them
+            *peers_done = rc == T81B200_OK;
+            return rc;
+        }
     }
     return gemm_trit_simt_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, st);
 }

@@ -22,6 +22,8 @@
 #include "common.cuh"
 #include "tma.cuh"
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace t81b200 {
@@ -40,7 +42,11 @@ constexpr int RAW_STAGE_BYTES = BM * 64;      // 4 limbs per row: 8 KB
 constexpr int NUM_THREADS = 14 * 32;
 constexpr int CONVERTER_WARP0 = 6;
 constexpr int CONVERTER_WARPS = 8;
-constexpr int SMEM_DATA_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + RAW_STAGES * RAW_STAGE_BYTES;
+constexpr int OUT_TOKENS = 32;                      // tokens per staged output block (one tcgen05.ld of 32 columns)
+constexpr int OUT_STAGE_BYTES = OUT_TOKENS * BM * 2;  // [token][feature] block of a 16-bit output type: 8 KB
+constexpr int OUT_STAGES = 2;
+constexpr int SMEM_DATA_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + RAW_STAGES * RAW_STAGE_BYTES +
+                                OUT_STAGES * OUT_STAGE_BYTES;
 constexpr int SMEM_BYTES = SMEM_DATA_BYTES + 256 /*barriers*/ + 1024 /*alignment slack*/;
 constexpr uint32_t TMEM_COLS = 512;
 
@@ -61,7 +67,23 @@ struct TcParams {
     int m_tiles, n_tiles, n_atoms;
     int plane_rows;  // row distance between the activation planes in the tensor map
     float alpha, beta;
+    int debug;
+    int n_out_maps;      // > 0: the epilogue stages output blocks in shared memory and stores them by TMA through
+                         // this many tensor maps (the local C first, then the peers'); 0: per-element stores
+    int n_peers;         // other GPUs that receive a copy of every output element
+    void *peer_C[T81B200_MAX_PEERS];  // their C, same strides as the local one
 };
+
+// Tensor maps of the result, for the TMA-store epilogue: [0] the local C, then one per peer.
+struct TcOutMaps {
+    CUtensorMap m[1 + T81B200_MAX_PEERS];
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
 
 // K-major, SWIZZLE_128B shared-memory descriptor: rows are 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -105,7 +127,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 // same expanded weights into the same accumulator, on a 128-token tile.
 template <typename CT, int PLANES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ TcOutMaps omaps, const TcParams p) {
     constexpr int BN = BN_MAX / PLANES;
     constexpr int PLANE_BYTES = BN * BK * 2;
     constexpr uint32_t kInstrDesc = instr_desc(BN);
@@ -114,7 +137,8 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t a_smem = base;
     const uint32_t b_smem = a_smem + A_STAGES * A_STAGE_BYTES;
     const uint32_t raw_smem = b_smem + B_STAGES * B_STAGE_BYTES;
-    const uint32_t bars = raw_smem + RAW_STAGES * RAW_STAGE_BYTES;
+    const uint32_t out_smem = raw_smem + RAW_STAGES * RAW_STAGE_BYTES;
+    const uint32_t bars = out_smem + OUT_STAGES * OUT_STAGE_BYTES;
     uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
     // barrier slots (8 bytes each)
     auto a_full = [&](int s) { return bars + 8u * s; };
@@ -218,6 +242,7 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int lane_group = warp & 3;  // TMEM lanes 32*lane_group .. +31 are this warp's
         bool ok = true;
         int it = 0;
+        int out_count = 0;  // staged output blocks so far (picks the staging buffer)
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
             const int buf = it & 1;
@@ -230,6 +255,32 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const float scale = (row_ok && p.row_scale ? p.row_scale[row] : 1.0f) * p.alpha;
             const float bias = row_ok && p.bias ? p.bias[row] : 0.0f;
             CT *crow = static_cast<CT *>(p.C) + row * p.c_row_stride;
+            if (p.n_out_maps > 0) {
+                // 16-bit output, token-major C: stage [32 tokens][128 features] blocks in shared memory and let
+                // TMA write them (whole 256-byte rows; the tensor map clips rows and tokens past the end)
+                const int epi_tid = threadIdx.x - 2 * 32;  // 0..127
+                uint8_t *stage0 = gen_base + (out_smem - base);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c, ++out_count) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN_MAX + c * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int sb = out_count & 1;
+                    // the stores issued from this buffer two blocks ago must have read it
+                    if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    CT *dst = reinterpret_cast<CT *>(stage0 + sb * OUT_STAGE_BYTES) + lane_group * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) dst[i * BM] = from_float<CT>(__uint_as_float(v[i]) * scale + bias);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (epi_tid == 0) {
+                        for (int j = 0; j < p.n_out_maps; ++j)
+                            tma_store_2d(&omaps.m[j], out_smem + (uint32_t)sb * OUT_STAGE_BYTES, m0, n0 + c * 32);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
@@ -239,11 +290,17 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int64_t tok = (int64_t)n0 + c * 32 + i;
-                        if (tok < p.N) {
+                        if (tok < p.N && (!(p.debug & 4) || v[i] == 0x12345u)) {
                             float y = __uint_as_float(v[i]) * scale + bias;
                             CT *dst = crow + tok * p.c_tok_stride;
                             if (p.beta != 0.0f) y += p.beta * to_float<CT>(*dst);
-                            *dst = from_float<CT>(y);
+                            const CT out = from_float<CT>(y);
+                            *dst = out;
+                            if (p.n_peers > 0) {
+                                // column-sharded Linear: the same element goes into every peer's result over NVLink
+                                const int64_t off = dst - static_cast<CT *>(p.C);
+                                for (int pj = 0; pj < p.n_peers; ++pj) static_cast<CT *>(p.peer_C[pj])[off] = out;
+                            }
                         }
                     }
                 }
@@ -252,6 +309,8 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));
         }
+        // every TMA store of this CTA has completed before the kernel ends
+        if (threadIdx.x == 2 * 32) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         if (!ok && lane == 0) atomicCAS(&g_tc_status, STATUS_OK, STATUS_TIMEOUT_EPILOGUE);
     } else {
         // ---------------- converters ----------------
@@ -289,21 +348,26 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const int item = cthread + 256 * h;
                     const int r = item >> 2, j = item & 3;
                     uint32_t o[24];
+                    uint32_t nat[24];
+                    if (p.debug & 1) {
+#pragma unroll
+                        for (int i = 0; i < 24; ++i) nat[i] = (&limb[h].x)[i & 3];
+                    } else {
                     decode_limb(limb[h], o);
                     // decode order -> natural order: pairs (trit 2m, trit 2m+1)
-                    uint32_t nat[24];
 #pragma unroll
                     for (int pr = 0; pr < 8; ++pr) {
                         nat[3 * pr + 0] = __byte_perm(o[3 * pr], o[3 * pr + 1], 0x5410);
                         nat[3 * pr + 1] = __byte_perm(o[3 * pr + 2], o[3 * pr], 0x7610);
                         nat[3 * pr + 2] = __byte_perm(o[3 * pr + 1], o[3 * pr + 2], 0x7632);
                     }
+                    }
                     const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
 #pragma unroll
                     for (int q = 0; q < 6; ++q) {
                         const int chunk = 6 * j + q;         // 16-byte chunk inside the 384-byte super-block row
                         const int atom = chunk >> 3, cc = chunk & 7;
-                        if (atom < atoms_here) {
+                        if (atom < atoms_here && (!(p.debug & 2) || nat[4 * q] == 0x12345u)) {
                             int st = a.stage + atom;
                             st = st >= A_STAGES ? st - A_STAGES : st;
                             const uint32_t off = (uint32_t)st * A_STAGE_BYTES + row_off + (uint32_t)((cc ^ (r & 7)) << 4);
@@ -336,7 +400,7 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 template <typename CT, int PLANES>
-int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, cudaStream_t st) {
+int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcOutMaps &om, const TcParams &p, cudaStream_t st) {
     auto kern = gemm_trit_tc_kernel<CT, PLANES>;
     static bool configured = false;
     if (!configured) {
@@ -344,18 +408,20 @@ int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, c
         configured = true;
     }
     const int tiles = p.m_tiles * p.n_tiles;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(mw, mx, p);
+    int sms = sm_count();
+    if (const char *env = getenv("T81B200_TC_SM_RESERVE")) { const int r = atoi(env); if (r > 0 && r < sms) sms -= r; }
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(mw, mx, om, p);
     T81_LAUNCH_CHECK("gemm_trit_tc_kernel");
     return T81B200_OK;
 }
 
 template <int PLANES>
-int launch_tc_ct(int c_dtype, const CUtensorMap &mw, const CUtensorMap &mx, const TcParams &p, cudaStream_t st) {
+int launch_tc_ct(int c_dtype, const CUtensorMap &mw, const CUtensorMap &mx, const TcOutMaps &om, const TcParams &p, cudaStream_t st) {
     switch (c_dtype) {
-        case T81B200_F32: return launch_tc<float, PLANES>(mw, mx, p, st);
-        case T81B200_BF16: return launch_tc<__nv_bfloat16, PLANES>(mw, mx, p, st);
-        case T81B200_F16: return launch_tc<__half, PLANES>(mw, mx, p, st);
+        case T81B200_F32: return launch_tc<float, PLANES>(mw, mx, om, p, st);
+        case T81B200_BF16: return launch_tc<__nv_bfloat16, PLANES>(mw, mx, om, p, st);
+        case T81B200_F16: return launch_tc<__half, PLANES>(mw, mx, om, p, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
 }
@@ -460,7 +526,8 @@ int gemm_trit_tc_status(int reset) {
 
 int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                         int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int64_t N,
-                        int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+                        int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t st,
+                        int n_peers, void *const *peer_C) {
     const TcPlan plan = make_plan(b_dtype, layout, N, K);
     const void *x_ptr = B;
     int64_t x_ld = ldb, x_rows = N;
@@ -499,7 +566,29 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
     p.n_atoms = (int)((K + BK - 1) / BK);
     p.plane_rows = (int)plan.rows_pad;
     p.alpha = alpha; p.beta = beta;
-    return plan.planes == 2 ? launch_tc_ct<2>(c_dtype, mw, mx, p, st) : launch_tc_ct<1>(c_dtype, mw, mx, p, st);
+    p.n_peers = n_peers;
+    for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.peer_C[i] = i < n_peers ? peer_C[i] : nullptr;
+    p.debug = getenv("T81B200_TC_DEBUG") ? atoi(getenv("T81B200_TC_DEBUG")) : 0;
+    // TMA-store epilogue: 16-bit output, token-major C (features contiguous), no read-modify-write, and every
+    // result 16-byte aligned with a 16-byte multiple as its row pitch
+    TcOutMaps om;
+    memset(&om, 0, sizeof om);
+    p.n_out_maps = 0;
+    const size_t esz = dtype_size(c_dtype);
+    bool tma_out = esz == 2 && layout == T81B200_LAYOUT_NK && beta == 0.0f && (ldc * 2) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(C) % 16 == 0 && !(getenv("T81B200_TC_EPILOGUE") && getenv("T81B200_TC_EPILOGUE")[0] == 'd');
+    for (int i = 0; i < n_peers; ++i) tma_out = tma_out && reinterpret_cast<uintptr_t>(peer_C[i]) % 16 == 0;
+    if (tma_out) {
+        const CUtensorMapDataType dt = c_dtype == T81B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        for (int i = 0; i <= n_peers; ++i) {
+            void *dst = i == 0 ? C : peer_C[i - 1];
+            if (int rc = make_map_2d(&om.m[i], dt, 2, dst, (uint64_t)M, (uint64_t)N, (uint64_t)ldc * 2, BM, OUT_TOKENS,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE))
+                return rc;
+        }
+        p.n_out_maps = 1 + n_peers;
+    }
+    return plan.planes == 2 ? launch_tc_ct<2>(c_dtype, mw, mx, om, p, st) : launch_tc_ct<1>(c_dtype, mw, mx, om, p, st);
 }
 
 }  // namespace t81b200

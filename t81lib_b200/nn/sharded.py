@@ -42,6 +42,62 @@ def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     return gathered.permute(1, 0, 2).reshape(tokens, world * per)
 
 
+class PeerColumns:
+    """Full-width (tokens, out_features) result buffers of every rank of one node, mapped into
+    this process, for an all-gather made of copy-engine pushes.
+
+    Each rank's matmul writes its output features straight into columns [lo, hi) of its own
+    buffer (a strided C operand) and, from the same kernel, into the same place of every
+    peer's buffer over NVLink (``ops.gemm_trit(..., peers=...)``); one tiny all-reduce
+    (``signal``) then tells every rank that all blocks have landed.  Compared with
+    ``all_gather_into_tensor`` there is no second pass over the result: no gather kernel and
+    no token-major re-copy of a rank-major gather buffer.
+
+    Construction is collective (handles are exchanged through the process group).  ``copies``
+    buffers are handed out round-robin so that a push may still be in flight while the next
+    matmul fills another buffer.  CUDA only; ranks must be processes of one node that see the
+    same GPUs in the same order."""
+
+    def __init__(self, tokens: int, out_features: int, dtype: torch.dtype, device: torch.device, group=None,
+                 copies: int = 2):
+        from torch.multiprocessing.reductions import reduce_tensor
+        if device.type != "cuda":
+            raise ValueError("PeerColumns needs CUDA tensors (there is no CPU path)")
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.tokens, self.out_features, self.dtype, self.device = tokens, out_features, dtype, device
+        self.buffers = [torch.empty((tokens, out_features), dtype=dtype, device=device) for _ in range(copies)]
+        mine = [reduce_tensor(b) for b in self.buffers]  # (rebuild function, CUDA IPC handle + geometry)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.peers = []  # peers[r][i]: rank r's buffer i as a tensor of this process (None for this rank)
+        for r, handles in enumerate(everyone):
+            # open the handle in THIS rank's device context (argument 6 of torch's rebuild function is
+            # the device index): kernels and copies of this GPU then reach the peer's memory over NVLink
+            self.peers.append(None if r == self.rank else
+                              [fn(*(args[:6] + (device.index,) + args[7:])) for fn, args in handles])
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self._next = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def next_index(self) -> int:
+        i = self._next
+        self._next = (i + 1) % len(self.buffers)
+        return i
+
+    def peer_blocks(self, index: int, lo: int, hi: int) -> list:
+        """Columns [lo, hi) of every peer's buffer ``index`` (views of peer memory), in an order
+        that starts with a different peer on every rank."""
+        return [self.peers[(self.rank + shift) % self.world][index][:, lo:hi] for shift in range(1, self.world)]
+
+    def signal(self) -> None:
+        """Queue, on torch's current stream, the all-reduce after which every rank's buffers hold
+        the column blocks that all ranks wrote before their own ``signal``."""
+        dist.all_reduce(self._flag, group=self.group)
+
+
 class ShardedLinear(nn.Module):
     """Eval-only ternary Linear whose rows are sharded over ``group``.
 
@@ -50,7 +106,7 @@ class ShardedLinear(nn.Module):
 
     def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, threshold: float = 0.45,
                  rule: str = "fixed", group=None, rank: Optional[int] = None, world_size: Optional[int] = None,
-                 shard_min_tokens: int = 0, matmul=None, quantize=None):
+                 shard_min_tokens: int = 0, exchange: str = "collective", matmul=None, quantize=None):
         super().__init__()
         if weight.ndim != 2:
             raise ValueError("t81.trit tensors currently only support 2D matrices")
@@ -66,6 +122,13 @@ class ShardedLinear(nn.Module):
         # of microseconds, a decode-sized matmul a few.  Needs the whole packed matrix on every
         # rank (2.67 bits per weight); the shard is then a view of it, not a second copy.
         self.shard_min_tokens = shard_min_tokens
+        # "collective": one all_gather_into_tensor per call (any backend).  "p2p": PeerColumns
+        # pushes over NVLink (CUDA, one node); the result is then a buffer owned by the module
+        # and reused two calls later.
+        if exchange not in ("collective", "p2p"):
+            raise ValueError(f"unknown exchange {exchange!r}")
+        self.exchange = exchange
+        self._exchanges: dict = {}
         self._full_matmul = None
         self._full_bias = None if bias is None or shard_min_tokens <= 0 else bias.detach().clone()
         # `quantize` / `matmul` are injection points for host-side tests of the sharding
@@ -111,7 +174,27 @@ class ShardedLinear(nn.Module):
             if bias is not None and bias.device != x.device:
                 bias = self._full_bias = bias.to(x.device)
             return self._full_matmul(x, bias)
+        if self.exchange == "p2p" and self.world_size > 1 and x.is_cuda and hasattr(self.ternary_weight, "packed"):
+            return self._forward_p2p(x)
         local = self.forward_local(x)
         if self.world_size == 1:
             return local
         return gather_columns(local, self.group)
+
+    def _forward_p2p(self, x: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+        tokens = x.shape[0]
+        key = (tokens, x.dtype)
+        ex = self._exchanges.get(key)
+        if ex is None:  # collective: every rank reaches this with the same shape
+            ex = self._exchanges[key] = PeerColumns(tokens, self.out_features, x.dtype, x.device, self.group)
+        i = ex.next_index()
+        lo, hi = self.rows
+        w = self.ternary_weight
+        bias = self.bias
+        if bias is not None and bias.device != x.device:
+            bias = self.bias = bias.to(x.device)
+        ops.gemm_trit(w.packed, x, M=hi - lo, K=self.in_features, layout="nk", row_scale=w.row_scale, bias=bias,
+                      C=ex.buffers[i][:, lo:hi], peers=ex.peer_blocks(i, lo, hi))
+        ex.signal()
+        return ex.buffers[i]

@@ -7,6 +7,7 @@ arithmetic happens in ``libt81_b200.so``.
 
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Tuple
 
 import torch
@@ -129,9 +130,12 @@ def gemm_limb(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, M: int, N: int,
 def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: str,
               row_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
               C: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
-              out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+              out_dtype: Optional[torch.dtype] = None, peers=None) -> torch.Tensor:
     """TRIT mode.  ``layout="kn"``: B is (K, N), result (M, N).  ``layout="nk"``:
-    B is (N, K) (one token per row), result (N, M)."""
+    B is (N, K) (one token per row), result (N, M).
+
+    ``peers``: tensors with C's shape, strides and dtype whose memory lives on other GPUs of
+    the node (mapped into this process); every element of C is written to them too."""
     _require_cuda(packed, "packed")
     _require_cuda(B, "B")
     if B.ndim != 2:
@@ -169,6 +173,19 @@ def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: 
     if bs is not None and (bs.dtype != torch.float32 or bs.device != dev or not bs.is_contiguous()):
         bs = bs.detach().to(device=dev, dtype=torch.float32).contiguous()
     direct = b_code == _capi.BF16 and code == _capi.LAYOUT_NK  # no scratch needed
+    if peers:
+        for t in peers:
+            if tuple(t.shape) != tuple(C.shape) or t.stride() != C.stride() or t.dtype != C.dtype:
+                raise ValueError("peer results must have C's shape, strides and dtype")
+        ptrs = (ctypes.c_void_p * len(peers))(*[t.data_ptr() for t in peers])
+        with torch.cuda.device(dev):
+            need = 0 if direct else _capi.lib.t81b200_gemm_trit_workspace_bytes(b_code, code, c_code, M, N, K)
+            ws = _workspace(dev, need)
+            _capi.check(_capi.lib.t81b200_gemm_trit_peers(
+                _ptr(packed), _ptr(rs), _ptr(B), b_code, code, ldb, _ptr(bs), _ptr(C), c_code, ldc,
+                M, N, K, float(alpha), float(beta), _ptr(ws), 0 if ws is None else ws.numel(), len(peers), ptrs,
+                _stream(dev)))
+        return C
     if direct and dev.index == torch.cuda.current_device():
         _capi.check(_capi.lib.t81b200_gemm_trit(
             packed.data_ptr(), _ptr(rs), B.data_ptr(), b_code, code, ldb, _ptr(bs), C.data_ptr(), c_code, ldc,
