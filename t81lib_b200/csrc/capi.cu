@@ -83,7 +83,6 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
 
 int gemm_trit_tc_status(int reset);
 int gemv_trit_status(int reset);
-int gemv_trit_umma_status(int reset);
 
 }  // namespace t81b200
 
@@ -93,8 +92,7 @@ extern "C" int t81b200_kernel_status(int reset) {
     if (int rc = check_device()) return rc;
     const int tc = gemm_trit_tc_status(reset);
     const int gv = gemv_trit_status(reset);
-    const int um = gemv_trit_umma_status(reset);
-    return tc != 0 ? tc : (gv != 0 ? gv : um);
+    return tc != 0 ? tc : gv;
 }
 
 extern "C" int t81b200_copy_columns(void *dst, int64_t dst_pitch, const void *src, int64_t src_pitch,

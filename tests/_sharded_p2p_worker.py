@@ -1,0 +1,54 @@
+"""One rank of tests/test_gpu_sharded_p2p.py (started by torch.distributed.run, one process per GPU):
+the column-sharded Linear with exchange="p2p" must return, on every rank, exactly what the unsharded
+layer returns, for the tensor-core path (stores into the peers from the GEMM), for fp32 activations
+(per-element peer stores) and for decode-sized calls (copy-engine push after the streaming kernel)."""
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from t81lib_b200 import _capi
+    from t81lib_b200 import torch as t81_torch
+    from t81lib_b200.nn.sharded import ShardedLinear
+
+    gen = torch.Generator(device=dev).manual_seed(5)  # same values on every rank
+    w = torch.randn(1024, 520, generator=gen, device=dev) * 0.02
+    b = torch.randn(1024, generator=gen, device=dev) * 0.01
+    full = t81_torch.TernaryTensor.from_float(w, threshold=0.45, rule="absmean")
+    ok = True
+    for tokens, dtype in ((300, torch.bfloat16), (8, torch.bfloat16), (130, torch.float32), (700, torch.float16)):
+        x = torch.randn(tokens, 520, generator=gen, device=dev).to(dtype)
+        want = full.matmul_input(x, bias=b)
+        for exchange in ("collective", "p2p"):
+            layer = ShardedLinear(w, b, threshold=0.45, rule="absmean", exchange=exchange)
+            for _ in range(3):  # the p2p buffers are handed out round-robin: go around more than once
+                got = layer(x)
+                torch.cuda.synchronize()
+                same = torch.equal(got, want)
+                ok = ok and same
+                if rank == 0 and not same:
+                    print(f"MISMATCH tokens={tokens} dtype={dtype} exchange={exchange}", flush=True)
+    ok = ok and _capi.kernel_status(reset=True) == 0
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("SHARDED_P2P_OK" if flag.item() == 1 else "SHARDED_P2P_FAILED", flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0 if flag.item() == 1 else 1)  # no process-group teardown (it has been seen to wait forever)
+
+
+if __name__ == "__main__":
+    main()

@@ -106,3 +106,24 @@ def test_gather_columns_single_rank_is_identity():
         assert gather_columns(t) is t
     finally:
         dist.destroy_process_group()
+
+
+def test_unknown_exchange_is_rejected():
+    w = torch.zeros(8, 16)
+    with pytest.raises(ValueError, match="unknown exchange"):
+        ShardedLinear(w, None, world_size=1, rank=0, exchange="carrier-pigeon", quantize=_cpu_quantize,
+                      matmul=lambda x, b: x)
+
+
+def test_p2p_exchange_is_a_cuda_only_path_and_cpu_inputs_take_the_collective():
+    # with CPU tensors (or injected kernels) exchange="p2p" must not try to map peer memory
+    gen = torch.Generator().manual_seed(3)
+    weight = torch.randn(12, 50, generator=gen) * 0.02
+    x = torch.randn(4, 50, generator=gen)
+    holder = {}
+    layer = ShardedLinear(weight, None, threshold=0.45, rule="absmean", world_size=1, rank=0, exchange="p2p",
+                          quantize=_cpu_quantize, matmul=_cpu_matmul_factory(holder))
+    holder["w"] = layer.ternary_weight
+    packed, scale = oracle.pack_dense_matrix_absmean(weight.numpy(), 0.45)
+    want = oracle.linear_forward(packed, scale, None, x.numpy(), 50)
+    assert np.array_equal(layer(x).numpy(), want)
