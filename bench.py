@@ -219,9 +219,8 @@ def run_ours(args):
         mods = []
         for name, out_f, in_f in LINEARS:
             w = torch.randn(out_f, in_f, generator=gen, device=dev) * 0.02  # same on every rank
-            # every rank packs the whole matrix (2.3 GB for the stack): prefill-sized calls use this
-            # rank's row slice of it (row-wise packing makes the slice a contiguous view), decode-sized
-            # calls are too short to pay for an all-gather and run unsharded on every rank
+            # every rank packs the whole matrix and uses its own row slice of it (row-wise packing makes
+            # the slice a contiguous view, byte for byte what packing the slice alone would give)
             packed, scale = ops.quantize_pack(w, THRESHOLD, "absmean")
             mods.append((name, out_f, in_f, packed, scale))
             del w
@@ -246,12 +245,20 @@ def run_ours(args):
 
     prefill_mods = [[shard(m) for m in mods] for mods in layers]
 
-    # Prefill with N > 1: each GEMM writes this rank's output features into their columns of its own
-    # full-width buffer and of every peer's (stores over NVLink from the kernel's epilogue); a side
-    # stream then runs the tiny all-reduce that tells every rank the blocks have landed, while the
-    # next Linear's GEMM runs.  Two buffers per width (ping-pong) keep a GEMM from overwriting a
-    # result whose exchange has not been signalled yet.
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    # Prefill with N > 1: every GEMM computes this rank's output features and writes them into their
+    # columns of its own full-width result AND of every peer's (TMA stores over NVLink from the kernel's
+    # epilogue); flag words written behind the data order the exchange (each call waits for the peers'
+    # stores of the previous call and signals its own; no collective, no host involvement).  One explicit
+    # wait closes the phase.  Two result buffers per width are used in turn.
+
+    def sharded_pass(x_by_width, bufs):
+        for mods in prefill_mods:
+            for name, out_l, in_f, packed, scale in mods:
+                ex = bufs[out_l * world]
+                idx = ex.next_index()
+                lo, hi = rank * out_l, (rank + 1) * out_l
+                ops.gemm_trit(packed, x_by_width[in_f], M=out_l, K=in_f, layout="nk", row_scale=scale,
+                              C=ex.buffers[idx][:, lo:hi], peers=ex.peer_blocks(idx, lo, hi), sync=ex.flags)
 
     def prefill():
         if world == 1:
@@ -259,30 +266,12 @@ def run_ours(args):
                 for name, out_f, in_f, packed, scale in mods:
                     ops.gemm_trit(packed, x_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=y_loc[out_f])
             return
-        compute = torch.cuda.current_stream(dev)
-        pushed = {}  # (width, buffer index) -> event: that buffer's exchange has finished
-        for mods in prefill_mods:
-            for name, out_l, in_f, packed, scale in mods:
-                full = out_l * world
-                ex = y_peer[full]
-                idx = ex.next_index()
-                lo, hi = rank * out_l, (rank + 1) * out_l
-                prev = pushed.get((full, idx))
-                if prev is not None:
-                    compute.wait_event(prev)
-                ops.gemm_trit(packed, x_in[in_f], M=out_l, K=in_f, layout="nk", row_scale=scale, C=ex.buffers[idx][:, lo:hi],
-                              peers=ex.peer_blocks(idx, lo, hi))
-                done = torch.cuda.Event()
-                done.record(compute)
-                with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(done)
-                    ex.signal()
-                    ev = torch.cuda.Event()
-                    ev.record(comm_stream)
-                pushed[(full, idx)] = ev
-        compute.wait_stream(comm_stream)
+        sharded_pass(x_in, y_peer)
+        y_peer[HIDDEN].flags.wait()
 
     def decode_step():
+        # decode runs whole on every rank at any N: the exchange adds ~8 us to a 5 us kernel (one system
+        # fence, one flag flight over NVLink, one poll), more than the rows a rank would save
         for mods in layers:
             for name, out_f, in_f, packed, scale in mods:
                 ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_loc[out_f])
@@ -352,22 +341,23 @@ def run_ours(args):
     roof = {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
             "frac": tf / pk["bf16_tflops_sustained"], "traffic": None, "peak_source": pk["source"] + " (sustained bf16)",
             "kernel": "gemm_trit_tc_kernel", "note": "prefill phase: 224 launches per step, includes launch gaps"
-                      + ("; includes the all-gather" if world > 1 else "")}
+                      + ("; includes the exchange" if world > 1 else "")}
     # decode: algorithmic bytes of the streaming kernel
-    packed_bytes = sum(m[3].numel() for mods in layers for m in mods)  # decode runs unsharded on every rank
+    packed_bytes = sum(m[3].numel() for mods in layers for m in mods)  # decode runs whole on every rank
     bytes_decode = packed_bytes + sum(4 * m[1] + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
     gbs = bytes_decode * DECODE / (dec_ms * 1e-3) / 1e9
     gemv = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
             "kernel": "gemv_trit_kernel", "tokens": dtok, "cuda_graph": graph is not None,
-            "note": "decode phase: 224 launches per step, includes launch gaps" + ("; unsharded on every rank" if world > 1 else "")}
+            "note": "decode phase: 224 launches per step, includes launch gaps" + ("; whole on every rank" if world > 1 else "")}
 
     launches = args.steps * (1 + DECODE) * LAYERS * len(LINEARS)
     line = {
         "metric": "t8.nn.Linear tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": (f"prefill: output features sharded x{world}, every output element also stored into each peer's result over NVLink by the GEMM epilogue, one small all-reduce per Linear as the completion signal; "
-                                   f"decode: unsharded on every rank (an all-gather costs more than the 8-token GEMV)") if world > 1 else "single GPU",
+        "config": {"workload": WORKLOAD, "parallelism": (f"prefill: output features of every Linear sharded x{world}, the GEMM epilogue also stores its output block into every peer's "
+                                   f"result over NVLink, flag words order the exchange (no collective); decode: whole on every rank (the exchange "
+                                   f"costs more than the rows saved)") if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 2.3 GB of packed weights and a 134 MB activation buffer are streamed each step",
                    "prefill_ms": pre_ms, "decode_ms": dec_ms, "prefill_tokens_per_s": ptok / (pre_ms * 1e-3),
                    "decode_tokens_per_s": dtok * DECODE / (dec_ms * 1e-3)},

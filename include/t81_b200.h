@@ -192,14 +192,31 @@ T81B200_API int t81b200_kernel_status(int reset);
  * whole: an all-gather without a second pass over the data.  The tensor-core kernel
  * stores to the peers from its epilogue (plain stores over NVLink while the next tile
  * is multiplied); the other kernels are followed by t81b200_copy_columns per peer.
- * beta applies to the local C only.  The caller orders "all ranks have finished" itself
- * (a barrier or flag exchange after the call).  No counterpart in the reference (it has
- * no multi-GPU path). */
+ * beta reads the local C only.
+ *
+ * Ordering between the ranks.  With sync_local == NULL the caller orders "all ranks have
+ * finished" itself (a barrier after the call).  Otherwise sync_local points to
+ * T81B200_SYNC_WORDS zero-initialised uint32 words in this GPU's memory that the peers
+ * can write, and sync_slots[j] is the address, inside peer j's words, of the slot that
+ * belongs to this rank: word 16 * (1 + i) when this rank is entry i of that peer's peer
+ * list.  The call then (1) waits, on the device, until every peer has signalled as many
+ * exchanges as this rank has completed, i.e. until what the peers stored for the previous
+ * call is in this GPU's memory, before it reads B; (2) after its own stores have been
+ * performed, publishes its new exchange count into its slot on every peer.  Chained
+ * calls on all ranks thus form an all-gather per call with no host involvement and no
+ * collective; the decode-sized kernel carries both steps inside the kernel, the others
+ * get a one-thread kernel before and after.  Every wait is bounded (t81b200_kernel_status
+ * reports an expired one).  t81b200_exchange_wait queues step (1) alone, for a consumer
+ * that is not one of these calls.  All ranks must issue the same sequence of calls.
+ * No counterpart in the reference (it has no multi-GPU path). */
 #define T81B200_MAX_PEERS 7
+#define T81B200_SYNC_WORDS 256
 T81B200_API int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale, const void *B, int b_dtype,
                             int layout, int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc,
                             int64_t M, int64_t N, int64_t K, float alpha, float beta, void *workspace,
-                            size_t workspace_bytes, int n_peers, void *const *peer_C, void *stream);
+                            size_t workspace_bytes, int n_peers, void *const *peer_C, uint32_t *sync_local,
+                            uint32_t *const *sync_slots, void *stream);
+T81B200_API int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *stream);
 
 /* Column-block copy for the column-sharded Linear: copies `rows` rows of `width_bytes`
  * bytes from src (row pitch src_pitch bytes) to dst (row pitch dst_pitch bytes) on the

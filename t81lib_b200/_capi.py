@@ -18,11 +18,14 @@ RULE_FIXED, RULE_ABSMEAN = 0, 1
 LAYOUT_KN, LAYOUT_NK = 0, 1
 STATIC_SCRATCH_BYTES = 16 << 20
 
+MAX_PEERS = 7       # T81B200_MAX_PEERS
+SYNC_WORDS = 256    # T81B200_SYNC_WORDS
+
 EXPORTS = (
     "t81b200_device_available", "t81b200_last_error", "t81b200_version", "t81b200_quantize_pack",
     "t81b200_quantize_trits", "t81b200_unpack", "t81b200_gemm_limb", "t81b200_gemm_limb_host",
     "t81b200_gemm_trit", "t81b200_gemm_trit_host", "t81b200_gemm_trit_static", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
-    "t81b200_copy_columns", "t81b200_gemm_trit_peers",
+    "t81b200_copy_columns", "t81b200_gemm_trit_peers", "t81b200_exchange_wait",
 )
 
 
@@ -63,7 +66,8 @@ def _load() -> ctypes.CDLL:
     lib.t81b200_kernel_status.argtypes = [ci]
     lib.t81b200_copy_columns.argtypes = [vp, i64, vp, i64, i64, i64, vp]
     lib.t81b200_gemm_trit_peers.argtypes = [vp, vp, vp, ci, ci, i64, vp, vp, ci, i64, i64, i64, i64, f32, f32,
-                                            vp, ctypes.c_size_t, ci, ctypes.POINTER(vp), vp]
+                                            vp, ctypes.c_size_t, ci, ctypes.POINTER(vp), vp, ctypes.POINTER(vp), vp]
+    lib.t81b200_exchange_wait.argtypes = [vp, ci, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is ctypes.c_int and name not in ("t81b200_device_available",):

@@ -70,7 +70,7 @@ int sm_count() {
 
 int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, int x_dtype, int64_t ldx,
                      const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int ntok, int64_t K,
-                     float alpha, float beta, cudaStream_t st);
+                     float alpha, float beta, cudaStream_t st, PeerCtx *ctx);
 int gemm_trit_simt_launch(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                           int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                           int64_t N, int64_t K, float alpha, float beta, cudaStream_t st);
@@ -126,21 +126,21 @@ extern "C" size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int
 static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                            int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                            int64_t N, int64_t K, float alpha, float beta, void *workspace,
-                           size_t workspace_bytes, void *stream, int n_peers, void *const *peer_C, bool *peers_done);
+                           size_t workspace_bytes, void *stream, PeerCtx *ctx);
 
 extern "C" int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                                  int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                                  int64_t N, int64_t K, float alpha, float beta, void *workspace,
                                  size_t workspace_bytes, void *stream) {
-    bool unused = false;
     return gemm_trit_local(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, workspace,
-                           workspace_bytes, stream, 0, nullptr, &unused);
+                           workspace_bytes, stream, nullptr);
 }
 
 extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                                        int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                                        int64_t N, int64_t K, float alpha, float beta, void *workspace,
-                                       size_t workspace_bytes, int n_peers, void *const *peer_C, void *stream) {
+                                       size_t workspace_bytes, int n_peers, void *const *peer_C, uint32_t *sync_local,
+                                       uint32_t *const *sync_slots, void *stream) {
     if (n_peers < 0 || n_peers > T81B200_MAX_PEERS)
         return fail(T81B200_ELIMIT, "gemm_trit_peers: %d peers, at most %d are supported", n_peers, T81B200_MAX_PEERS);
     if (int rc = check_device()) return rc;
@@ -148,6 +148,7 @@ extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale,
     T81_CUDA_TRY(cudaGetDevice(&cur));
     for (int i = 0; i < n_peers; ++i) {
         if (!peer_C || !peer_C[i]) return fail(T81B200_EINVAL, "gemm_trit_peers: null peer pointer");
+        if (sync_local && (!sync_slots || !sync_slots[i])) return fail(T81B200_EINVAL, "gemm_trit_peers: null flag slot");
         // the kernels store to these addresses: they must be device memory this GPU can reach
         cudaPointerAttributes attr;
         T81_CUDA_TRY(cudaPointerGetAttributes(&attr, peer_C[i]));
@@ -162,23 +163,34 @@ extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale,
             else if (e != cudaSuccess) return fail(T81B200_ECUDA, "gemm_trit_peers: enabling peer access to GPU %d: %s", attr.device, cudaGetErrorString(e));
         }
     }
-    bool peers_done = false;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PeerCtx ctx;
+    ctx.n_peers = n_peers; ctx.peer_C = peer_C; ctx.sync_local = sync_local; ctx.sync_slots = sync_slots;
+    if (M == 0 || N == 0) return T81B200_OK;
     if (int rc = gemm_trit_local(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta,
-                                 workspace, workspace_bytes, stream, n_peers, peer_C, &peers_done))
+                                 workspace, workspace_bytes, stream, &ctx))
         return rc;
-    if (peers_done || n_peers == 0 || M == 0 || N == 0) return T81B200_OK;
-    // a kernel without peer stores produced C: push the block with the copy engines instead
-    const int64_t esz = (int64_t)dtype_size(c_dtype);
-    const int64_t rows = layout == T81B200_LAYOUT_NK ? N : M, width = (layout == T81B200_LAYOUT_NK ? M : N) * esz;
-    for (int i = 0; i < n_peers; ++i)
-        if (int rc = t81b200_copy_columns(peer_C[i], ldc * esz, C, ldc * esz, width, rows, stream)) return rc;
+    if (!ctx.peers_done && n_peers > 0) {
+        // a kernel without peer stores produced C: push the block with the copy engines instead
+        const int64_t esz = (int64_t)dtype_size(c_dtype);
+        const int64_t rows = layout == T81B200_LAYOUT_NK ? N : M, width = (layout == T81B200_LAYOUT_NK ? M : N) * esz;
+        for (int i = 0; i < n_peers; ++i)
+            if (int rc = t81b200_copy_columns(peer_C[i], ldc * esz, C, ldc * esz, width, rows, stream)) return rc;
+    }
+    if (sync_local && !ctx.sync_fused) return exchange_signal_launch(sync_local, sync_slots, n_peers, st);
     return T81B200_OK;
+}
+
+extern "C" int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *stream) {
+    if (int rc = check_device()) return rc;
+    if (!sync_local || n_peers < 0 || n_peers > T81B200_MAX_PEERS) return fail(T81B200_EINVAL, "exchange_wait: bad arguments");
+    return exchange_wait_launch(sync_local, n_peers, static_cast<cudaStream_t>(stream));
 }
 
 static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                            int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                            int64_t N, int64_t K, float alpha, float beta, void *workspace,
-                           size_t workspace_bytes, void *stream, int n_peers, void *const *peer_C, bool *peers_done) {
+                           size_t workspace_bytes, void *stream, PeerCtx *ctx) {
     if (M < 0 || N < 0 || K < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
     if (!valid_dtype(b_dtype) || !valid_dtype(c_dtype)) return fail(T81B200_EINVAL, "gemm_trit: unknown dtype");
     if (layout != T81B200_LAYOUT_KN && layout != T81B200_LAYOUT_NK)
@@ -197,16 +209,23 @@ static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void 
     const char *small_n = getenv("T81B200_SMALLN_PATH");
     const bool small_n_tc = small_n && small_n[0] == 't' && b_dtype == T81B200_BF16;
     if (a_aligned && layout == T81B200_LAYOUT_NK && N <= 16 && K > 0 && !small_n_tc)
-        return gemv_trit_launch(A, row_scale, B, b_dtype, ldb, bias, C, c_dtype, ldc, M, (int)N, K, alpha, beta, st);
+        return gemv_trit_launch(A, row_scale, B, b_dtype, ldb, bias, C, c_dtype, ldc, M, (int)N, K, alpha, beta, st, ctx);
+
+    // the other kernels do not carry the exchange protocol: wait for the peers' stores before they read
+    if (ctx && ctx->sync_local && !ctx->waited) {
+        if (int rc = exchange_wait_launch(ctx->sync_local, ctx->n_peers, st)) return rc;
+        ctx->waited = true;
+    }
 
     if (a_aligned && gemm_trit_tc_eligible(b_dtype, layout, c_dtype, M, N, K)) {
         const size_t need = gemm_trit_tc_workspace(b_dtype, layout, c_dtype, M, N, K);
         if (need > 0 && (!workspace || workspace_bytes < need))
             return fail(T81B200_EWORKSPACE, "gemm_trit: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
         const int rc = gemm_trit_tc_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K,
-                                           alpha, beta, workspace, workspace_bytes, st, n_peers, peer_C);
+                                           alpha, beta, workspace, workspace_bytes, st, ctx ? ctx->n_peers : 0,
+                                           ctx ? ctx->peer_C : nullptr);
         if (rc != T81B200_EALIGN) {  // unaligned activations: the general kernel takes them
-            *peers_done = rc == T81B200_OK;
+            if (ctx) ctx->peers_done = rc == T81B200_OK;
             return rc;
         }
     }

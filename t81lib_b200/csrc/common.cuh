@@ -18,6 +18,19 @@ namespace t81b200 {
 void set_error(const char *fmt, ...);
 int fail(int code, const char *fmt, ...);
 int check_device();  // T81B200_OK or T81B200_ENODEVICE (cached per process)
+// Column-sharded Linear: where the result also goes, and the flags that order the exchange.
+struct PeerCtx {
+    int n_peers = 0;
+    void *const *peer_C = nullptr;           // the peers' results (same strides as the local C)
+    uint32_t *sync_local = nullptr;          // this rank's exchange flags, or null
+    uint32_t *const *sync_slots = nullptr;   // this rank's slot in each peer's flags
+    bool peers_done = false;                 // set by a launcher whose kernel stored into the peers itself
+    bool sync_fused = false;                 // ... and waited / signalled inside the kernel
+    bool waited = false;                     // a stand-alone wait has been queued before the kernel
+};
+int exchange_wait_launch(const uint32_t *sync_local, int n_peers, cudaStream_t st);
+int exchange_signal_launch(uint32_t *sync_local, uint32_t *const *slots, int n_peers, cudaStream_t st);
+
 int sm_count();      // multiprocessors of the current device (cached per device)
 
 #define T81_CUDA_TRY(expr)                                                              \

@@ -44,7 +44,53 @@ struct GemvParams {
     int row_groups;         // RG: 16-row groups each row-warp walks in sequence
     int row_warps;          // RW: warps side by side along the rows; W/RW warps split the contraction
     float alpha, beta;
+    int n_peers;            // other GPUs whose result receives every output element too
+    void *peer_C[T81B200_MAX_PEERS];
 };
+
+// ---- exchange flags of the column-sharded Linear ----------------------------------------------
+// sync_local (this GPU's memory, T81B200_SYNC_WORDS words, zero at start):
+//   [0] CTAs of the running kernel that have finished storing   [1] exchanges this rank has completed
+//   [16 * (1 + j)] the sequence number peer j has published here
+// A kernel that stores into the peers ends with exchange_signal (the last CTA publishes the new
+// sequence number into each peer's slot); a kernel that reads what the peers stored starts with
+// exchange_wait.  Every wait is bounded.
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ bool exchange_wait(const uint32_t *sync_local, int n_peers) {
+    const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(sync_local + 1);
+    for (int j = 0; j < n_peers; ++j) {
+        const uint32_t *flag = sync_local + 16 * (1 + j);
+        bool seen = false;
+        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+            if ((int32_t)(ld_acquire_sys(flag) - expected) >= 0) { seen = true; break; }
+            if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
+        }
+        if (!seen) return false;
+    }
+    return true;
+}
+
+// Called by one thread per CTA after the CTA's stores and a CTA barrier.
+__device__ __forceinline__ void exchange_signal(uint32_t *sync_local, uint32_t *const *sync_peer, int n_peers,
+                                                uint32_t total_ctas) {
+    __threadfence_system();
+    const uint32_t old = atomicAdd(sync_local, 1u);
+    if (old == total_ctas - 1) {
+        *reinterpret_cast<volatile uint32_t *>(sync_local) = 0u;
+        const uint32_t seq = *reinterpret_cast<volatile uint32_t *>(sync_local + 1) + 1u;
+        *reinterpret_cast<volatile uint32_t *>(sync_local + 1) = seq;
+        __threadfence_system();
+        for (int j = 0; j < n_peers; ++j) st_release_sys(sync_peer[j], seq);
+    }
+}
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -127,7 +173,9 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int64_t row, int 
     if (p.bias) v += p.bias[row];
     CT *c = static_cast<CT *>(p.C) + (int64_t)tok * p.ldc + row;
     if (p.beta != 0.0f) v += p.beta * to_float<CT>(*c);
-    *c = from_float<CT>(v);
+    const CT out = from_float<CT>(v);
+    *c = out;
+    for (int pj = 0; pj < p.n_peers; ++pj) static_cast<CT *>(p.peer_C[pj])[(int64_t)tok * p.ldc + row] = out;
 }
 
 template <typename XT> struct Planes { static constexpr int value = 2; };
@@ -290,10 +338,13 @@ __global__ void __launch_bounds__(WARPS * 32, VAR == 1 ? (WARPS == 8 ? 4 : 2) : 
     // CTA per cluster, the ranks' partials through distributed shared memory.
     const int outs = rows_per_cta * kTokPad;
     if (slices == 1) {
-        for (int idx = threadIdx.x; idx < outs; idx += THREADS) {
+        for (int o = threadIdx.x; o < outs; o += THREADS) {
+            // with peers: rows fastest, so that a warp stores runs of consecutive rows of one token over NVLink
+            const int r = p.n_peers > 0 ? o % rows_per_cta : o / kTokPad, tk = p.n_peers > 0 ? o / rows_per_cta : o % kTokPad;
+            const int idx = r * kTokPad + tk;
             float s = part[idx];
             for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
-            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+            store_out<CT>(p, cta_row0 + r, tk, s);
         }
     } else {
         for (int idx = threadIdx.x; idx < outs; idx += THREADS) {
@@ -306,10 +357,12 @@ __global__ void __launch_bounds__(WARPS * 32, VAR == 1 ? (WARPS == 8 ? 4 : 2) : 
         const int span = (rows_per_cta + slices - 1) / slices;
         const int lo = slice * span;
         const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
-        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += THREADS) {
+        for (int o = threadIdx.x; o < (hi - lo) * kTokPad; o += THREADS) {
+            const int r = lo + (p.n_peers > 0 ? o % (hi - lo) : o / kTokPad), tk = p.n_peers > 0 ? o / (hi - lo) : o % kTokPad;
+            const int idx = r * kTokPad + tk;
             float s = 0.0f;
             for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
-            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+            store_out<CT>(p, cta_row0 + r, tk, s);
         }
         cluster.sync();  // peers may still be reading this CTA's partials
     }
@@ -373,7 +426,7 @@ constexpr int kTmaMaxConsumerWarps = 16;
 constexpr int kTmaMaxThreads = (kTmaMaxConsumerWarps + 1) * 32;
 constexpr int kTmaMaxStages = 48;
 
-enum { GEMV_STATUS_OK = 0, GEMV_STATUS_TIMEOUT_PRODUCER = 5, GEMV_STATUS_TIMEOUT_CONSUMER = 6 };
+enum { GEMV_STATUS_OK = 0, GEMV_STATUS_TIMEOUT_PRODUCER = 5, GEMV_STATUS_TIMEOUT_CONSUMER = 6, GEMV_STATUS_TIMEOUT_EXCHANGE = 7 };
 __device__ int g_gemv_status = 0;
 
 struct GemvTmaParams {
@@ -384,6 +437,8 @@ struct GemvTmaParams {
     int ring_offset;   // bytes from the start of dynamic shared memory (128-byte aligned)
     int part_offset;   // bytes: partial sums, KW x rows x tokpad floats
     int bar_offset;    // bytes: full[stages], empty[stages]
+    uint32_t *sync_local;                     // exchange flags (null: no exchange protocol in this launch)
+    uint32_t *sync_peer[T81B200_MAX_PEERS];   // this rank's slot in each peer's flags
 };
 
 template <typename XT, typename CT, int TOKB>
@@ -457,6 +512,12 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
         rw = warp % p.row_warps;
         kw = warp / p.row_warps;
         asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
+        if (tp.sync_local) {
+            // ... or what the peers stored into this GPU's memory: wait until all of them have published
+            if (threadIdx.x == 0 && !exchange_wait(tp.sync_local, p.n_peers))
+                atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_EXCHANGE);
+            asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");
+        }
         stage_activations<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride, consumer_threads);
         asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // consumers only; the producer is already streaming
 
@@ -520,10 +581,13 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
 
     const int outs = rows_per_cta * kTokPad;
     if (slices == 1) {
-        for (int idx = threadIdx.x; idx < outs; idx += all_threads) {
+        for (int o = threadIdx.x; o < outs; o += all_threads) {
+            // with peers: rows fastest, so that a warp stores runs of consecutive rows of one token over NVLink
+            const int r = p.n_peers > 0 ? o % rows_per_cta : o / kTokPad, tk = p.n_peers > 0 ? o / rows_per_cta : o % kTokPad;
+            const int idx = r * kTokPad + tk;
             float s = part[idx];
             for (int w = 1; w < k_warps; ++w) s += part[(size_t)w * outs + idx];
-            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+            store_out<CT>(p, cta_row0 + r, tk, s);
         }
     } else {
         for (int idx = threadIdx.x; idx < outs; idx += all_threads) {
@@ -535,13 +599,34 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
         const int span = (rows_per_cta + slices - 1) / slices;
         const int lo = slice * span;
         const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
-        for (int idx = lo * kTokPad + threadIdx.x; idx < hi * kTokPad; idx += all_threads) {
+        for (int o = threadIdx.x; o < (hi - lo) * kTokPad; o += all_threads) {
+            const int r = lo + (p.n_peers > 0 ? o % (hi - lo) : o / kTokPad), tk = p.n_peers > 0 ? o / (hi - lo) : o % kTokPad;
+            const int idx = r * kTokPad + tk;
             float s = 0.0f;
             for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
-            store_out<CT>(p, cta_row0 + idx / kTokPad, idx % kTokPad, s);
+            store_out<CT>(p, cta_row0 + r, tk, s);
         }
         cluster.sync();
     }
+    if (tp.sync_local) {
+        // one system fence per CTA, by the signalling thread after the barrier (a fence in every
+        // thread costs ten times the kernel): the barrier orders the CTA's stores before it
+        __syncthreads();
+        if (threadIdx.x == 0) exchange_signal(tp.sync_local, tp.sync_peer, p.n_peers, gridDim.x * gridDim.y);
+    }
+}
+
+// The same protocol as separate launches, around kernels that do not carry it themselves.
+__global__ void exchange_wait_kernel(const uint32_t *sync_local, int n_peers) {
+    if (threadIdx.x == 0 && !exchange_wait(sync_local, n_peers))
+        atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_EXCHANGE);
+}
+
+struct SignalSlots {
+    uint32_t *slot[T81B200_MAX_PEERS];
+};
+__global__ void exchange_signal_kernel(uint32_t *sync_local, SignalSlots slots, int n_peers) {
+    if (threadIdx.x == 0) exchange_signal(sync_local, slots.slot, n_peers, 1u);
 }
 
 template <typename XT, typename CT, int TOKB>
@@ -590,9 +675,11 @@ size_t gemv_smem_bytes(int planes, int ntok, int tokpad, int lps, int warps, int
 
 // Shape choice and launch of the TMA-fed kernel.  Returns T81B200_EALIGN when no configuration
 // fits (the caller then uses the register-prefetch kernel).
-int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaStream_t st) {
+int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaStream_t st, const PeerCtx *ctx) {
     GemvTmaParams tp;
     tp.g = base;
+    tp.sync_local = ctx ? ctx->sync_local : nullptr;
+    for (int i = 0; i < T81B200_MAX_PEERS; ++i) tp.sync_peer[i] = tp.sync_local && i < ctx->n_peers ? ctx->sync_slots[i] : nullptr;
     const int ntok = base.ntok;
     const int planes = x_dtype == T81B200_BF16 ? 1 : 2;
     const int tokpad = ntok > 8 ? 16 : 8;
@@ -666,6 +753,20 @@ int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaS
     return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
 }
 
+int exchange_wait_launch(const uint32_t *sync_local, int n_peers, cudaStream_t st) {
+    exchange_wait_kernel<<<1, 32, 0, st>>>(sync_local, n_peers);
+    T81_LAUNCH_CHECK("exchange_wait_kernel");
+    return T81B200_OK;
+}
+
+int exchange_signal_launch(uint32_t *sync_local, uint32_t *const *slots, int n_peers, cudaStream_t st) {
+    SignalSlots sl;
+    for (int i = 0; i < T81B200_MAX_PEERS; ++i) sl.slot[i] = i < n_peers ? slots[i] : nullptr;
+    exchange_signal_kernel<<<1, 32, 0, st>>>(sync_local, sl, n_peers);
+    T81_LAUNCH_CHECK("exchange_signal_kernel");
+    return T81B200_OK;
+}
+
 int gemv_trit_status(int reset) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemv_status, sizeof v) != cudaSuccess) return T81B200_ECUDA;
@@ -682,11 +783,14 @@ namespace {
 // Host entry used by the dispatcher in capi.cu.  NK layout, ntok in 1..16, A 16-byte aligned.
 int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, int x_dtype, int64_t ldx,
                      const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int ntok, int64_t K,
-                     float alpha, float beta, cudaStream_t st) {
+                     float alpha, float beta, cudaStream_t st, PeerCtx *ctx) {
     GemvParams p;
     p.A = A; p.X = X; p.row_scale = row_scale; p.bias = bias; p.C = C;
     p.M = M; p.K = K; p.kl = (K + 47) / 48; p.ldx = ldx; p.ldc = ldc; p.ntok = ntok;
     p.alpha = alpha; p.beta = beta;
+    p.n_peers = ctx ? ctx->n_peers : 0;
+    for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.peer_C[i] = i < p.n_peers ? ctx->peer_C[i] : nullptr;
+    if (ctx) ctx->peers_done = true;  // both streaming kernels store into the peers themselves
     const int planes = x_dtype == T81B200_BF16 ? 1 : 2;
     const int tokpad = ntok > 8 ? 16 : 8;
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
@@ -695,8 +799,15 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     const char *path = getenv("T81B200_GEMV_PATH");
     if (!(path && path[0] == 'l')) {
         p.row_warps = 1; p.row_groups = 1; p.limbs_per_slice = 4;
-        const int rc = gemv_trit_tma_launch(p, x_dtype, c_dtype, st);
-        if (rc != T81B200_EALIGN) return rc;
+        const int rc = gemv_trit_tma_launch(p, x_dtype, c_dtype, st, ctx);
+        if (rc != T81B200_EALIGN) {
+            if (ctx && ctx->sync_local && rc == T81B200_OK) ctx->sync_fused = true;
+            return rc;
+        }
+    }
+    if (ctx && ctx->sync_local) {  // the register-prefetch kernel does not carry the exchange protocol
+        if (int rc = exchange_wait_launch(ctx->sync_local, ctx->n_peers, st)) return rc;
+        ctx->waited = true;
     }
 
     // Pick the CTA shape with a small cost model.  A CTA has W warps arranged as RW row groups

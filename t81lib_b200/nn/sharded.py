@@ -42,14 +42,70 @@ def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     return gathered.permute(1, 0, 2).reshape(tokens, world * per)
 
 
+def _open_on(device: torch.device, handles):
+    """Rebuild tensors another rank exported with ``reduce_tensor``, opening the CUDA IPC handle in
+    THIS rank's device context (argument 6 of torch's rebuild function is the device index): kernels
+    and copies of this GPU then reach the peer's memory over NVLink."""
+    return [fn(*(args[:6] + (device.index,) + args[7:])) for fn, args in handles]
+
+
+class ExchangeFlags:
+    """The flag words that order the exchanges of column-sharded Linears between the GPUs of one
+    node without a collective and without the host: every rank owns ``SYNC_WORDS`` words that its
+    peers can write, and knows the address of its own slot in every peer's words (layout: see
+    ``t81b200_gemm_trit_peers``).  One instance per (group, device), shared by every exchange on
+    that device, because a call waits for the peers' PREVIOUS call whatever layer that was.
+    Construction is collective."""
+
+    _instances: dict = {}
+
+    @classmethod
+    def get(cls, device: torch.device, group=None) -> "ExchangeFlags":
+        key = (device.index, id(group) if group is not None else None)
+        inst = cls._instances.get(key)
+        if inst is None:
+            inst = cls._instances[key] = cls(device, group)
+        return inst
+
+    def __init__(self, device: torch.device, group=None):
+        import ctypes
+        from torch.multiprocessing.reductions import reduce_tensor
+        from .. import _capi
+        self.device, self.group = device, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world - 1 > _capi.MAX_PEERS:
+            raise ValueError(f"at most {_capi.MAX_PEERS + 1} ranks are supported")
+        self.words = torch.zeros(_capi.SYNC_WORDS, dtype=torch.int32, device=device)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, [reduce_tensor(self.words)], group=group)
+        self.peer_ranks = [(self.rank + shift) % self.world for shift in range(1, self.world)]
+        self._peer_words = {r: _open_on(device, everyone[r])[0] for r in self.peer_ranks}
+        slots = []
+        for q in self.peer_ranks:
+            i = (self.rank - q - 1) % self.world  # this rank's position in q's peer list
+            slots.append(self._peer_words[q].data_ptr() + 4 * 16 * (1 + i))
+        self.local_ptr = self.words.data_ptr()
+        self.slot_ptrs = (ctypes.c_void_p * len(slots))(*slots)
+        self.n_peers = len(slots)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def wait(self) -> None:
+        """Queue, on torch's current stream, the wait after which everything the peers stored for
+        the calls issued so far is in this GPU's memory."""
+        from .. import _capi
+        _capi.check(_capi.lib.t81b200_exchange_wait(self.local_ptr, self.n_peers,
+                                                    torch.cuda.current_stream(self.device).cuda_stream))
+
+
 class PeerColumns:
     """Full-width (tokens, out_features) result buffers of every rank of one node, mapped into
     this process, for an all-gather made of copy-engine pushes.
 
     Each rank's matmul writes its output features straight into columns [lo, hi) of its own
     buffer (a strided C operand) and, from the same kernel, into the same place of every
-    peer's buffer over NVLink (``ops.gemm_trit(..., peers=...)``); one tiny all-reduce
-    (``signal``) then tells every rank that all blocks have landed.  Compared with
+    peer's buffer over NVLink (``ops.gemm_trit(..., peers=..., sync=flags)``); flag words written
+    behind the data (``ExchangeFlags``) tell every rank when all blocks have landed.  Compared with
     ``all_gather_into_tensor`` there is no second pass over the result: no gather kernel and
     no token-major re-copy of a rank-major gather buffer.
 
@@ -73,10 +129,8 @@ class PeerColumns:
         dist.all_gather_object(everyone, mine, group=group)
         self.peers = []  # peers[r][i]: rank r's buffer i as a tensor of this process (None for this rank)
         for r, handles in enumerate(everyone):
-            # open the handle in THIS rank's device context (argument 6 of torch's rebuild function is
-            # the device index): kernels and copies of this GPU then reach the peer's memory over NVLink
-            self.peers.append(None if r == self.rank else
-                              [fn(*(args[:6] + (device.index,) + args[7:])) for fn, args in handles])
+            self.peers.append(None if r == self.rank else _open_on(device, handles))
+        self.flags = ExchangeFlags.get(device, group)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         self._next = 0
         torch.cuda.synchronize(device)
@@ -93,8 +147,9 @@ class PeerColumns:
         return [self.peers[(self.rank + shift) % self.world][index][:, lo:hi] for shift in range(1, self.world)]
 
     def signal(self) -> None:
-        """Queue, on torch's current stream, the all-reduce after which every rank's buffers hold
-        the column blocks that all ranks wrote before their own ``signal``."""
+        """Collective alternative to the flag protocol: queue, on torch's current stream, an
+        all-reduce after which every rank's buffers hold the column blocks that all ranks wrote
+        before their own ``signal`` (for matmuls issued without ``sync=``)."""
         dist.all_reduce(self._flag, group=self.group)
 
 
@@ -128,6 +183,9 @@ class ShardedLinear(nn.Module):
         if exchange not in ("collective", "p2p"):
             raise ValueError(f"unknown exchange {exchange!r}")
         self.exchange = exchange
+        # p2p only: True leaves the wait for the peers' blocks to the consumer — the next sharded matmul
+        # waits at its start by itself; anything else calls ExchangeFlags.wait() first
+        self.defer_wait = False
         self._exchanges: dict = {}
         self._full_matmul = None
         self._full_bias = None if bias is None or shard_min_tokens <= 0 else bias.detach().clone()
@@ -195,6 +253,7 @@ class ShardedLinear(nn.Module):
         if bias is not None and bias.device != x.device:
             bias = self.bias = bias.to(x.device)
         ops.gemm_trit(w.packed, x, M=hi - lo, K=self.in_features, layout="nk", row_scale=w.row_scale, bias=bias,
-                      C=ex.buffers[i][:, lo:hi], peers=ex.peer_blocks(i, lo, hi))
-        ex.signal()
+                      C=ex.buffers[i][:, lo:hi], peers=ex.peer_blocks(i, lo, hi), sync=ex.flags)
+        if not self.defer_wait:
+            ex.flags.wait()
         return ex.buffers[i]

@@ -130,12 +130,14 @@ def gemm_limb(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, M: int, N: int,
 def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: str,
               row_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
               C: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0,
-              out_dtype: Optional[torch.dtype] = None, peers=None) -> torch.Tensor:
+              out_dtype: Optional[torch.dtype] = None, peers=None, sync=None) -> torch.Tensor:
     """TRIT mode.  ``layout="kn"``: B is (K, N), result (M, N).  ``layout="nk"``:
     B is (N, K) (one token per row), result (N, M).
 
     ``peers``: tensors with C's shape, strides and dtype whose memory lives on other GPUs of
-    the node (mapped into this process); every element of C is written to them too."""
+    the node (mapped into this process); every element of C is written to them too.  ``sync``:
+    an object with ``local_ptr`` and ``slot_ptrs`` (see ``nn.sharded.ExchangeFlags``): the call then
+    waits on the device for the peers' previous stores and signals its own."""
     _require_cuda(packed, "packed")
     _require_cuda(B, "B")
     if B.ndim != 2:
@@ -184,7 +186,7 @@ def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: 
             _capi.check(_capi.lib.t81b200_gemm_trit_peers(
                 _ptr(packed), _ptr(rs), _ptr(B), b_code, code, ldb, _ptr(bs), _ptr(C), c_code, ldc,
                 M, N, K, float(alpha), float(beta), _ptr(ws), 0 if ws is None else ws.numel(), len(peers), ptrs,
-                _stream(dev)))
+                None if sync is None else sync.local_ptr, None if sync is None else sync.slot_ptrs, _stream(dev)))
         return C
     if direct and dev.index == torch.cuda.current_device():
         _capi.check(_capi.lib.t81b200_gemm_trit(

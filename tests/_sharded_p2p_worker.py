@@ -26,7 +26,8 @@ def main() -> int:
     b = torch.randn(1024, generator=gen, device=dev) * 0.01
     full = t81_torch.TernaryTensor.from_float(w, threshold=0.45, rule="absmean")
     ok = True
-    for tokens, dtype in ((300, torch.bfloat16), (8, torch.bfloat16), (130, torch.float32), (700, torch.float16)):
+    for tokens, dtype in ((300, torch.bfloat16), (8, torch.bfloat16), (130, torch.float32), (700, torch.float16),
+                          (20, torch.float32), (3, torch.float32)):
         x = torch.randn(tokens, 520, generator=gen, device=dev).to(dtype)
         want = full.matmul_input(x, bias=b)
         for exchange in ("collective", "p2p"):
@@ -38,6 +39,15 @@ def main() -> int:
                 ok = ok and same
                 if rank == 0 and not same:
                     print(f"MISMATCH tokens={tokens} dtype={dtype} exchange={exchange}", flush=True)
+    # chained calls: each matmul waits for the peers' previous stores by itself, one wait at the end
+    x = torch.randn(8, 520, generator=gen, device=dev).to(torch.bfloat16)
+    want = full.matmul_input(x, bias=b)
+    layer = ShardedLinear(w, b, threshold=0.45, rule="absmean", exchange="p2p")
+    layer.defer_wait = True
+    outs = [layer(x) for _ in range(40)]
+    layer._exchanges[(8, torch.bfloat16)].flags.wait()
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(outs[-1], want) and torch.equal(outs[-2], want)
     ok = ok and _capi.kernel_status(reset=True) == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
