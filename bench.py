@@ -487,14 +487,76 @@ def quantize_pack_line(torch, dev, ops, pk):
             "frac": alg / sec / 1e9 / pk["hbm_gbs"], "us_per_launch": sec * 1e6, "kernel": "quantize_pack_kernel"}
 
 
+def run_kernel_case(args):
+    """One kernel alone on a small fixed case whose operands are larger than L2 (a few hundred MB):
+    the command the ncu captures under profiles/ are taken with, and a quick per-kernel figure.
+      gemv     : 14336 x 4096 (gate/up), 8 bf16 tokens, 16 distinct weight matrices, 2 passes
+      gemm     : 4096 x 4096, 16384 bf16 tokens, 3 launches
+      quantize : 4096 x 4096 fp32, absmean/0.45, 8 distinct matrices, 2 passes"""
+    import torch
+    from t81lib_b200 import _capi, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    assert _capi.device_available(), _capi.last_error()
+    pk = peaks()
+    gen = torch.Generator(device=dev).manual_seed(7)
+    if args.kernel == "gemv":
+        rows, k, tok = FFN, HIDDEN, BATCH
+        kl = (k + 47) // 48
+        mats = [torch.randint(0, 27, (rows, kl, 16), dtype=torch.uint8, device=dev, generator=gen) for _ in range(16)]
+        scale = torch.rand(rows, device=dev, generator=gen)
+        x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
+        y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
+        calls = [lambda m=m: ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=scale, C=y) for m in mats] * 2
+        alg, unit, peak, name = rows * kl * 16 + 4 * rows + 2 * tok * k + 2 * tok * rows, "GB/s", pk["hbm_gbs"], "gemv_trit_tma_kernel"
+    elif args.kernel == "gemm":
+        rows, k, tok = HIDDEN, HIDDEN, BATCH * PREFILL
+        kl = (k + 47) // 48
+        m = torch.randint(0, 27, (rows, kl, 16), dtype=torch.uint8, device=dev, generator=gen)
+        scale = torch.rand(rows, device=dev, generator=gen)
+        x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
+        y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
+        calls = [lambda: ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=scale, C=y)] * 3
+        alg, unit, peak, name = 2.0 * rows * k * tok, "TFLOP/s", pk["bf16_tflops"], "gemm_trit_tc_kernel"
+    else:
+        ws = [torch.randn(4096, 4096, device=dev, generator=gen) * 0.02 for _ in range(8)]
+        outs = [ops.quantize_pack(w, THRESHOLD, "absmean") for w in ws]
+        calls = [lambda w=w, o=o: ops.quantize_pack(w, THRESHOLD, "absmean", out=o[0], row_scale_out=o[1]) for w, o in zip(ws, outs)] * 2
+        alg, unit, peak, name = 4096 * 4096 * 4 + 4096 * 86 * 16 + 4096 * 4, "GB/s", pk["hbm_gbs"], "quantize_pack_row_kernel"
+    calls[0]()
+    torch.cuda.synchronize()
+    graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):  # the kernels are shorter than a Python-side launch
+            for c in calls:
+                c()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) * 1e-3 / len(calls)
+    assert _capi.kernel_status(reset=True) == 0
+    achieved = alg / sec / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"kernel": name, "case": args.kernel, "launches": len(calls), "us_per_launch": sec * 1e6,
+                      "achieved": achieved, "unit": unit, "peak": peak, "frac": achieved / peak,
+                      "peak_source": pk["source"] + (" (burst bf16)" if unit == "TFLOP/s" else "")}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", choices=["gemv", "gemm", "quantize"], default=None,
+                    help="time one kernel alone on a small case instead of the whole job (used for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel:
+        run_kernel_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -62,6 +62,16 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB_PATH
     os.makedirs(_LIBDIR, exist_ok=True)
+    # one builder at a time: the ranks of a multi-GPU job import the package at the same moment
+    import fcntl
+    with open(os.path.join(_LIBDIR, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not _stale():
+            return LIB_PATH
+        return _build_locked(verbose)
+
+
+def _build_locked(verbose: bool) -> str:
     objdir = os.path.join(_LIBDIR, "obj")
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()

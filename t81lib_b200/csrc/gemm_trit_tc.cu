@@ -38,10 +38,16 @@ constexpr int B_STAGES = 3;
 constexpr int RAW_STAGES = 2;
 constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
 constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;  // 32 KB: one 256-token plane or two 128-token planes
+#ifndef T81B200_TC_CONVERTER_WARPS
+#define T81B200_TC_CONVERTER_WARPS 8
+#endif
+constexpr int CONVERTER_WARPS_ = T81B200_TC_CONVERTER_WARPS;
 constexpr int RAW_STAGE_BYTES = BM * 64;      // 4 limbs per row: 8 KB
-constexpr int NUM_THREADS = 14 * 32;
+constexpr int NUM_THREADS = (6 + CONVERTER_WARPS_) * 32;
 constexpr int CONVERTER_WARP0 = 6;
-constexpr int CONVERTER_WARPS = 8;
+constexpr int CONVERTER_WARPS = CONVERTER_WARPS_;
+constexpr int CONVERTER_THREADS = CONVERTER_WARPS * 32;
+constexpr int LIMBS_PER_CONVERTER = BM * 4 / CONVERTER_THREADS;  // limbs of a 4-limb super-block per thread
 constexpr int OUT_TOKENS = 32;                      // tokens per staged output block (one tcgen05.ld of 32 columns)
 constexpr int OUT_STAGE_BYTES = OUT_TOKENS * BM * 2;  // [token][feature] block of a 16-bit output type: 8 KB
 constexpr int OUT_STAGES = 2;
@@ -323,10 +329,10 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int s = 0; s < n_super && ok; ++s) {
                 ok = __all_sync(0xffffffffu, mbar_wait(raw_full(raw.stage), raw.phase));
                 if (!ok) break;
-                uint4 limb[2];
+                uint4 limb[LIMBS_PER_CONVERTER];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int item = cthread + 256 * h;  // row = item / 4, limb = item % 4
+                for (int h = 0; h < LIMBS_PER_CONVERTER; ++h) {
+                    const int item = cthread + CONVERTER_THREADS * h;  // row = item / 4, limb = item % 4
                     limb[h] = *reinterpret_cast<const uint4 *>(gen_base + A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES +
                                                                raw.stage * RAW_STAGE_BYTES + item * 16);
                     if ((int64_t)4 * s + (item & 3) >= p.kl)  // past the row's last limb: zero trits
@@ -346,8 +352,8 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int item = cthread + 256 * h;
+                for (int h = 0; h < LIMBS_PER_CONVERTER; ++h) {
+                    const int item = cthread + CONVERTER_THREADS * h;
                     const int r = item >> 2, j = item & 3;
                     uint32_t o[24];
                     decode_limb(limb[h], o);
