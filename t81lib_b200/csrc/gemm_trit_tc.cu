@@ -305,7 +305,7 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     // column-sharded Linear: the same elements go into every peer's result over NVLink
                     for (int pj = 0; pj < p.n_peers; ++pj) {
                         CT *prow = static_cast<CT *>(p.peer_C[pj]) + row * p.c_row_stride;
-#pragma unroll
+#pragma unroll 1  // a rare path: unrolled it costs the whole kernel 40 registers
                         for (int i = 0; i < 32; ++i) {
                             const int64_t tok = (int64_t)n0 + c * 32 + i;
                             if (tok < p.N) prow[tok * p.c_tok_stride] = crow[tok * p.c_tok_stride];
