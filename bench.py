@@ -545,16 +545,72 @@ def run_kernel_case(args):
                       "peak_source": pk["source"] + (" (burst bf16)" if unit == "TFLOP/s" else "")}), flush=True)
 
 
+def run_sweep(args):
+    """BASELINE configs 3 and 4: the ternary Linear layers of a Phi-3-mini-shaped block, decode-sized calls with
+    1, 4 and 16 tokens (GB/s of algorithmic bytes against the HBM peak) and a 2048-token prefill with an fp32
+    bias (TFLOP/s against the bf16 tensor peak).  One JSON line per shape and token count; every figure is a
+    CUDA-graph replay over enough distinct weight matrices to exceed L2."""
+    import torch
+    from t81lib_b200 import _capi, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    assert _capi.device_available(), _capi.last_error()
+    pk = peaks()
+    gen = torch.Generator(device=dev).manual_seed(11)
+    shapes = [("qkv", 9216, 3072), ("o", 3072, 3072), ("gate_up", 16384, 3072), ("down", 3072, 8192)]
+    stream = torch.cuda.Stream(device=dev)
+    for name, rows, k in shapes:
+        kl = (k + 47) // 48
+        nbytes = rows * kl * 16
+        copies = max(2, int(400e6 // nbytes))
+        ws = [torch.randn(rows, k, device=dev, generator=gen) * 0.02 for _ in range(2)]
+        mats = [ops.quantize_pack(ws[i % 2], THRESHOLD, "absmean") for i in range(copies)]
+        bias = torch.randn(rows, device=dev, generator=gen) * 0.01
+        for tok in (1, 4, 16, 2048):
+            x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
+            y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
+            n = copies if tok <= 16 else 4
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                ops.gemm_trit(mats[0][0], x, M=rows, K=k, layout="nk", row_scale=mats[0][1], bias=bias, C=y)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(n):
+                        m, sc = mats[i % copies]
+                        ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=sc, bias=bias, C=y)
+                graph.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(3):
+                    graph.replay()
+                e1.record(stream)
+                torch.cuda.synchronize()
+            sec = e0.elapsed_time(e1) * 1e-3 / (3 * n)
+            if tok <= 16:
+                alg = nbytes + 8 * rows + 2 * tok * k + 2 * tok * rows
+                line = {"achieved": alg / sec / 1e9, "unit": "GB/s", "peak": pk["hbm_gbs"], "bound": "hbm"}
+            else:
+                line = {"achieved": 2.0 * rows * k * tok / sec / 1e12, "unit": "TFLOP/s", "peak": pk["bf16_tflops"], "bound": "tensor"}
+            line.update({"layer": name, "rows": rows, "k": k, "tokens": tok, "us_per_launch": sec * 1e6,
+                         "frac": line["achieved"] / line["peak"]})
+            print(json.dumps(line), flush=True)
+        del mats, ws
+    assert _capi.kernel_status(reset=True) == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=["gemv", "gemm", "quantize"], default=None,
+    ap.add_argument("--kernel", choices=["gemv", "gemm", "quantize", "sweep"], default=None,
                     help="time one kernel alone on a small case instead of the whole job (used for ncu captures)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
-    if args.kernel:
+    if args.kernel == "sweep":
+        run_sweep(args)
+    elif args.kernel:
         run_kernel_case(args)
     elif args.impl == "reference":
         run_reference(args)
