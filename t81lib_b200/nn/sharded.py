@@ -49,6 +49,18 @@ def _open_on(device: torch.device, handles):
     return [fn(*(args[:6] + (device.index,) + args[7:])) for fn, args in handles]
 
 
+def peer_order(rank: int, world: int) -> list:
+    """The other ranks in the order this rank lists them (a different first peer on every rank, so
+    that pushes do not all start on the same GPU)."""
+    return [(rank + shift) % world for shift in range(1, world)]
+
+
+def flag_slot_word(rank: int, peer: int, world: int) -> int:
+    """Index, inside ``peer``'s flag words, of the word ``rank`` publishes its exchange count to:
+    word 16 * (1 + i) where i is ``rank``'s position in ``peer``'s peer list."""
+    return 16 * (1 + (rank - peer - 1) % world)
+
+
 class ExchangeFlags:
     """The flag words that order the exchanges of column-sharded Linears between the GPUs of one
     node without a collective and without the host: every rank owns ``SYNC_WORDS`` words that its
@@ -78,12 +90,9 @@ class ExchangeFlags:
         self.words = torch.zeros(_capi.SYNC_WORDS, dtype=torch.int32, device=device)
         everyone = [None] * self.world
         dist.all_gather_object(everyone, [reduce_tensor(self.words)], group=group)
-        self.peer_ranks = [(self.rank + shift) % self.world for shift in range(1, self.world)]
+        self.peer_ranks = peer_order(self.rank, self.world)
         self._peer_words = {r: _open_on(device, everyone[r])[0] for r in self.peer_ranks}
-        slots = []
-        for q in self.peer_ranks:
-            i = (self.rank - q - 1) % self.world  # this rank's position in q's peer list
-            slots.append(self._peer_words[q].data_ptr() + 4 * 16 * (1 + i))
+        slots = [self._peer_words[q].data_ptr() + 4 * flag_slot_word(self.rank, q, self.world) for q in self.peer_ranks]
         self.local_ptr = self.words.data_ptr()
         self.slot_ptrs = (ctypes.c_void_p * len(slots))(*slots)
         self.n_peers = len(slots)
@@ -144,7 +153,7 @@ class PeerColumns:
     def peer_blocks(self, index: int, lo: int, hi: int) -> list:
         """Columns [lo, hi) of every peer's buffer ``index`` (views of peer memory), in an order
         that starts with a different peer on every rank."""
-        return [self.peers[(self.rank + shift) % self.world][index][:, lo:hi] for shift in range(1, self.world)]
+        return [self.peers[r][index][:, lo:hi] for r in peer_order(self.rank, self.world)]
 
     def signal(self) -> None:
         """Collective alternative to the flag protocol: queue, on torch's current stream, an

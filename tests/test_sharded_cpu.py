@@ -127,3 +127,18 @@ def test_p2p_exchange_is_a_cuda_only_path_and_cpu_inputs_take_the_collective():
     packed, scale = oracle.pack_dense_matrix_absmean(weight.numpy(), 0.45)
     want = oracle.linear_forward(packed, scale, None, x.numpy(), 50)
     assert np.array_equal(layer(x).numpy(), want)
+
+
+def test_exchange_flag_slots_are_consistent_between_ranks():
+    # Rank q waits on words 16 * (1 + j), j = 0 .. world-2, one per entry of ITS peer list; rank r must
+    # publish into exactly the word that stands for r in q's list, and no two ranks may share a word.
+    from t81lib_b200 import _capi
+    from t81lib_b200.nn.sharded import flag_slot_word, peer_order
+    for world in (2, 3, 4, 8):
+        assert world - 1 <= _capi.MAX_PEERS
+        for q in range(world):
+            order = peer_order(q, world)
+            assert sorted(order) == [r for r in range(world) if r != q]
+            words = [flag_slot_word(r, q, world) for r in order]
+            assert words == [16 * (1 + j) for j in range(world - 1)]  # q's j-th peer writes q's j-th wait word
+            assert max(words) < _capi.SYNC_WORDS and len(set(words)) == world - 1
