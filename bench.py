@@ -24,6 +24,7 @@ Prints ONE JSON line on rank 0.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -41,6 +42,7 @@ HIDDEN, KV, FFN = 4096, 1024, 14336
 # (name, out_features, in_features)
 LINEARS = [("q", HIDDEN, HIDDEN), ("k", KV, HIDDEN), ("v", KV, HIDDEN), ("o", HIDDEN, HIDDEN),
            ("gate", FFN, HIDDEN), ("up", FFN, HIDDEN), ("down", HIDDEN, FFN)]
+INDEPENDENT = ("k", "v", "up")  # Linears of a decoder block that read what their predecessor reads
 BATCH, PREFILL, DECODE = 8, 2048, 128
 THRESHOLD = 0.45
 WORKLOAD = ("llama3-8b-shaped ternary Linear stack: 32 layers x (q,o 4096x4096; k,v 1024x4096; gate,up 14336x4096; "
@@ -234,7 +236,7 @@ def run_ours(args):
     xd_in = {HIDDEN: x_in[HIDDEN][:dtok].contiguous(), FFN: x_in[FFN][:dtok].contiguous()}
     out_widths = sorted({o for _, o, _ in LINEARS})
     y_loc = {o: torch.empty(ptok, o // world, dtype=torch.bfloat16, device=dev) for o in out_widths}
-    yd_loc = {o: torch.empty(dtok, o, dtype=torch.bfloat16, device=dev) for o in out_widths}
+    yd_out = {name: torch.empty(dtok, o, dtype=torch.bfloat16, device=dev) for name, o, _ in LINEARS}  # one per Linear of a block
     # N > 1: full-width results of every rank, mapped into every process (copy-engine all-gather)
     y_peer = {o: PeerColumns(ptok, o, torch.bfloat16, dev) for o in out_widths} if world > 1 else None
 
@@ -272,9 +274,12 @@ def run_ours(args):
     def decode_step():
         # decode runs whole on every rank at any N: the exchange adds ~8 us to a 5 us kernel (one system
         # fence, one flag flight over NVLink, one poll), more than the rows a rank would save
+        # k, v read what q reads and up reads what gate reads: they need not wait for that predecessor
+        # (the decoder block's own data flow; every other Linear runs behind the one before it)
         for mods in layers:
             for name, out_f, in_f, packed, scale in mods:
-                ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_loc[out_f])
+                with ops.independent_of_previous() if name in INDEPENDENT else contextlib.nullcontext():
+                    ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_out[name])
 
     # the decode step is launch-bound: capture it once in a CUDA graph
     stream = torch.cuda.Stream(device=dev)
@@ -393,6 +398,7 @@ def e2e_public_api(torch, dev, Linear, layers, args):
     """Same job through nn.Module calls: pinned host activations are copied in for the
     prefill and for every decode step, the last Linear's output is copied back."""
     import t81lib_b200.torch as t81_torch
+    from t81lib_b200 import ops
     mods = []
     for layer in layers:
         row = []
@@ -413,8 +419,11 @@ def e2e_public_api(torch, dev, Linear, layers, args):
         y = None
         with torch.no_grad():
             for row in mods:
+                keep = []  # a block's outputs stay alive together, so k/v (up) never reuse q's (gate's) memory
                 for (name, out_f, in_f), m in zip(LINEARS, row):
-                    y = m(x[in_f])
+                    with ops.independent_of_previous() if name in INDEPENDENT else contextlib.nullcontext():
+                        y = m(x[in_f])
+                    keep.append(y)
         return y
 
     def forward(host, out_host):

@@ -218,6 +218,16 @@ T81B200_API int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale
                             uint32_t *const *sync_slots, void *stream);
 T81B200_API int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *stream);
 
+/* Scheduling hint for the calling thread, in force until changed: while it is on, each
+ * t81b200_gemm_trit call promises that it reads nothing (activations, bias, scales) that
+ * the PREVIOUS kernel queued on the same stream wrote, and writes nothing that kernel
+ * reads or writes - e.g. the k and v projections behind q, or up behind gate, which
+ * share their input.  The decode-sized kernel then starts its work while its
+ * predecessor is still running instead of behind it; it still does not complete before
+ * the predecessor has, so later calls can rely on stream order as usual.  Other kernels
+ * ignore the hint.  No counterpart in the reference. */
+T81B200_API void t81b200_hint_independent(int on);
+
 /* Column-block copy for the column-sharded Linear: copies `rows` rows of `width_bytes`
  * bytes from src (row pitch src_pitch bytes) to dst (row pitch dst_pitch bytes) on the
  * copy engines, stream-ordered.  dst may be memory of another GPU of the same node

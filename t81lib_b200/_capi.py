@@ -25,7 +25,7 @@ EXPORTS = (
     "t81b200_device_available", "t81b200_last_error", "t81b200_version", "t81b200_quantize_pack",
     "t81b200_quantize_trits", "t81b200_unpack", "t81b200_gemm_limb", "t81b200_gemm_limb_host",
     "t81b200_gemm_trit", "t81b200_gemm_trit_host", "t81b200_gemm_trit_static", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
-    "t81b200_copy_columns", "t81b200_gemm_trit_peers", "t81b200_exchange_wait",
+    "t81b200_copy_columns", "t81b200_gemm_trit_peers", "t81b200_exchange_wait", "t81b200_hint_independent",
 )
 
 
@@ -68,6 +68,8 @@ def _load() -> ctypes.CDLL:
     lib.t81b200_gemm_trit_peers.argtypes = [vp, vp, vp, ci, ci, i64, vp, vp, ci, i64, i64, i64, i64, f32, f32,
                                             vp, ctypes.c_size_t, ci, ctypes.POINTER(vp), vp, ctypes.POINTER(vp), vp]
     lib.t81b200_exchange_wait.argtypes = [vp, ci, vp]
+    lib.t81b200_hint_independent.argtypes = [ci]
+    lib.t81b200_hint_independent.restype = None
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is ctypes.c_int and name not in ("t81b200_device_available",):

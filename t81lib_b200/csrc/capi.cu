@@ -181,6 +181,10 @@ extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale,
     return T81B200_OK;
 }
 
+namespace t81b200 { extern thread_local int g_hint_independent; }
+
+extern "C" void t81b200_hint_independent(int on) { t81b200::g_hint_independent = on ? 1 : 0; }
+
 extern "C" int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *stream) {
     if (int rc = check_device()) return rc;
     if (!sync_local || n_peers < 0 || n_peers > T81B200_MAX_PEERS) return fail(T81B200_EINVAL, "exchange_wait: bad arguments");

@@ -437,6 +437,7 @@ struct GemvTmaParams {
     int ring_offset;   // bytes from the start of dynamic shared memory (128-byte aligned)
     int part_offset;   // bytes: partial sums, KW x rows x tokpad floats
     int bar_offset;    // bytes: full[stages], empty[stages]
+    int independent;   // 1: reads nothing the previous kernel of the stream wrote (see t81b200_hint_independent)
     uint32_t *sync_local;                     // exchange flags (null: no exchange protocol in this launch)
     uint32_t *sync_peer[T81B200_MAX_PEERS];   // this rank's slot in each peer's flags
 };
@@ -481,7 +482,11 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
     // Programmatic dependent launch: the next kernel in the stream may start now (it will wait
     // for this one where it needs to).  The weight stream below depends on no earlier kernel,
     // so it starts before the wait; activations, C and every store come after it.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A kernel that depends on its predecessor lets its own successor start only once its input is
+    // complete (after its wait below); one that does not depend on it has nothing to wait for here:
+    // it lets the successor start at once and waits for the predecessor at its very end instead, so
+    // that "this grid has completed" still implies "everything before it has".
+    if (tp.independent) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Several accumulator sets: consecutive MMAs of a chunk do not wait for one another.
     constexpr int NACC = 4;
@@ -506,12 +511,18 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
             }
             if (!ok) atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_PRODUCER);
         }
-        asm volatile("griddepcontrol.wait;" ::: "memory");  // before this warp's share of the output stores
+        if (!tp.independent) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // before this warp's share of the output stores
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
     } else {
         // ---------------- consumers ----------------
         rw = warp % p.row_warps;
         kw = warp / p.row_warps;
-        asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
+        if (!tp.independent) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
         if (tp.sync_local) {
             // ... or what the peers stored into this GPU's memory: wait until all of them have published
             if (threadIdx.x == 0 && !exchange_wait(tp.sync_local, p.n_peers))
@@ -608,6 +619,7 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
         }
         cluster.sync();
     }
+    if (tp.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tp.sync_local) {
         // one system fence per CTA, by the signalling thread after the barrier (a fence in every
         // thread costs ten times the kernel): the barrier orders the CTA's stores before it
@@ -675,9 +687,12 @@ size_t gemv_smem_bytes(int planes, int ntok, int tokpad, int lps, int warps, int
 
 // Shape choice and launch of the TMA-fed kernel.  Returns T81B200_EALIGN when no configuration
 // fits (the caller then uses the register-prefetch kernel).
+extern thread_local int g_hint_independent;
+
 int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaStream_t st, const PeerCtx *ctx) {
     GemvTmaParams tp;
     tp.g = base;
+    tp.independent = (g_hint_independent && !(ctx && ctx->sync_local)) ? 1 : 0;
     tp.sync_local = ctx ? ctx->sync_local : nullptr;
     for (int i = 0; i < T81B200_MAX_PEERS; ++i) tp.sync_peer[i] = tp.sync_local && i < ctx->n_peers ? ctx->sync_slots[i] : nullptr;
     const int ntok = base.ntok;
@@ -752,6 +767,8 @@ int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaS
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
 }
+
+thread_local int g_hint_independent = 0;
 
 int exchange_wait_launch(const uint32_t *sync_local, int n_peers, cudaStream_t st) {
     exchange_wait_kernel<<<1, 32, 0, st>>>(sync_local, n_peers);

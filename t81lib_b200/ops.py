@@ -7,6 +7,7 @@ arithmetic happens in ``libt81_b200.so``.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Optional, Tuple
 
@@ -59,6 +60,19 @@ def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+@contextlib.contextmanager
+def independent_of_previous():
+    """While active, every ``gemm_trit`` call issued by this thread promises that it reads nothing the
+    previous kernel on its stream wrote and writes nothing that kernel touches (k and v behind q, up
+    behind gate: same input, different outputs).  Decode-sized calls then start while their
+    predecessor still runs; completion order is unchanged, so later calls need no extra care."""
+    _capi.lib.t81b200_hint_independent(1)
+    try:
+        yield
+    finally:
+        _capi.lib.t81b200_hint_independent(0)
 
 
 def quantize_pack(w: torch.Tensor, threshold: float = 0.5, rule: str = "fixed",

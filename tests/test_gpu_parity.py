@@ -2,6 +2,7 @@
 fixtures generated from the reference.  Integer/byte results must be bit-exact;
 float results are compared at the tolerances written next to each check."""
 
+import contextlib
 import numpy as np
 import pytest
 import torch
@@ -416,3 +417,54 @@ def test_module_to_trit_patches_stock_linear(dev):
         model[2].weight.zero_()
     y2 = model(x)
     assert torch.allclose(y2, model[2].bias.expand_as(y2))
+
+
+def test_independence_hint_overlaps_launches_without_changing_results(dev):
+    """q, k, v share their input; with the hint on k and v they no longer wait for their predecessor.  A fourth,
+    ordinary call consumes q's output, so it must still see q complete.  Replayed many times from a CUDA graph,
+    the results must equal the plain chain bit for bit and agree with the oracle."""
+    from t81lib_b200 import ops
+    rng = np.random.default_rng(77)
+    in_f, sizes = 1000, {"q": 384, "k": 130, "v": 130}
+    packs = {}
+    for name, out_f in sizes.items():
+        w = rng.normal(0, 0.02, (out_f, in_f)).astype(np.float32)
+        packs[name] = (*oracle.pack_dense_matrix_absmean(w, 0.45), out_f)
+    w4 = rng.normal(0, 0.02, (200, 384)).astype(np.float32)
+    p4, s4 = oracle.pack_dense_matrix_absmean(w4, 0.45)
+    x_np = rng.normal(size=(8, in_f)).astype(np.float32)
+    x = torch.from_numpy(x_np).to(dev).to(torch.bfloat16)
+    dv = {n: (torch.from_numpy(p).to(dev), torch.from_numpy(s).to(dev), o) for n, (p, s, o) in packs.items()}
+    p4d, s4d = torch.from_numpy(p4).to(dev), torch.from_numpy(s4).to(dev)
+
+    def chain(hint, outs):
+        for name in ("q", "k", "v"):
+            p, s, o = dv[name]
+            ctx = ops.independent_of_previous() if hint and name != "q" else contextlib.nullcontext()
+            with ctx:
+                ops.gemm_trit(p, x, M=o, K=in_f, layout="nk", row_scale=s, C=outs[name])
+        ops.gemm_trit(p4d, outs["q"], M=200, K=384, layout="nk", row_scale=s4d, C=outs["o"])
+
+    results = {}
+    for hint in (False, True):
+        outs = {n: torch.zeros(8, o, dtype=torch.bfloat16, device=dev) for n, o in sizes.items()}
+        outs["o"] = torch.zeros(8, 200, dtype=torch.bfloat16, device=dev)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            chain(hint, outs)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(6):
+                    chain(hint, outs)
+            for _ in range(20):
+                graph.replay()
+            torch.cuda.synchronize()
+        results[hint] = {n: t.clone() for n, t in outs.items()}
+    for n in results[False]:
+        assert torch.equal(results[False][n], results[True][n]), n
+    want_q = oracle.linear_forward(packs["q"][0], packs["q"][1], None, x.float().cpu().numpy(), in_f)
+    got_q = results[True]["q"].float().cpu().numpy()
+    np.testing.assert_allclose(got_q, want_q, rtol=1e-2, atol=1e-2 * float(np.sqrt((want_q ** 2).mean())))
+    from t81lib_b200 import _capi
+    assert _capi.kernel_status(reset=True) == 0
