@@ -205,8 +205,9 @@ T81B200_API int t81b200_kernel_status(int reset);
  * performed, publishes its new exchange count into its slot on every peer.  Chained
  * calls on all ranks thus form an all-gather per call with no host involvement and no
  * collective; the decode-sized kernel carries both steps inside the kernel, the others
- * get a one-thread kernel before and after.  Every wait is bounded (t81b200_kernel_status
- * reports an expired one).  t81b200_exchange_wait queues step (1) alone, for a consumer
+ * get a one-thread kernel before and after.  Every wait is bounded (a few seconds;
+ * t81b200_kernel_status reports an expired one, word 2 of sync_local becomes non-zero and
+ * every later wait on that rank gives up at once, until the caller clears the words).  t81b200_exchange_wait queues step (1) alone, for a consumer
  * that is not one of these calls.  All ranks must issue the same sequence of calls.
  * No counterpart in the reference (it has no multi-GPU path). */
 #define T81B200_MAX_PEERS 7

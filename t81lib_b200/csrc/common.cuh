@@ -28,7 +28,7 @@ struct PeerCtx {
     bool sync_fused = false;                 // ... and waited / signalled inside the kernel
     bool waited = false;                     // a stand-alone wait has been queued before the kernel
 };
-int exchange_wait_launch(const uint32_t *sync_local, int n_peers, cudaStream_t st);
+int exchange_wait_launch(uint32_t *sync_local, int n_peers, cudaStream_t st);
 int exchange_signal_launch(uint32_t *sync_local, uint32_t *const *slots, int n_peers, cudaStream_t st);
 
 int sm_count();      // multiprocessors of the current device (cached per device)

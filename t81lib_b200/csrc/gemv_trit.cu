@@ -51,6 +51,7 @@ struct GemvParams {
 // ---- exchange flags of the column-sharded Linear ----------------------------------------------
 // sync_local (this GPU's memory, T81B200_SYNC_WORDS words, zero at start):
 //   [0] CTAs of the running kernel that have finished storing   [1] exchanges this rank has completed
+//   [2] non-zero once a wait has expired on this rank
 //   [16 * (1 + j)] the sequence number peer j has published here
 // A kernel that stores into the peers ends with exchange_signal (the last CTA publishes the new
 // sequence number into each peer's slot); a kernel that reads what the peers stored starts with
@@ -64,16 +65,22 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ bool exchange_wait(const uint32_t *sync_local, int n_peers) {
+__device__ __forceinline__ bool exchange_wait(uint32_t *sync_local, int n_peers) {
     const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(sync_local + 1);
+    // [2]: a wait on this rank has expired before (a peer is gone or out of step).  Later waits give up at
+    // once, so a lost peer costs one time limit (a few seconds), not one per call.
+    if (*reinterpret_cast<const volatile uint32_t *>(sync_local + 2) != 0u) return false;
     for (int j = 0; j < n_peers; ++j) {
         const uint32_t *flag = sync_local + 16 * (1 + j);
         bool seen = false;
-        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+        for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
             if ((int32_t)(ld_acquire_sys(flag) - expected) >= 0) { seen = true; break; }
             if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
         }
-        if (!seen) return false;
+        if (!seen) {
+            *reinterpret_cast<volatile uint32_t *>(sync_local + 2) = 1u;
+            return false;
+        }
     }
     return true;
 }
@@ -629,7 +636,7 @@ gemv_trit_tma_kernel(const __grid_constant__ CUtensorMap map_w, const GemvTmaPar
 }
 
 // The same protocol as separate launches, around kernels that do not carry it themselves.
-__global__ void exchange_wait_kernel(const uint32_t *sync_local, int n_peers) {
+__global__ void exchange_wait_kernel(uint32_t *sync_local, int n_peers) {
     if (threadIdx.x == 0 && !exchange_wait(sync_local, n_peers))
         atomicCAS(&g_gemv_status, GEMV_STATUS_OK, GEMV_STATUS_TIMEOUT_EXCHANGE);
 }
@@ -770,7 +777,7 @@ int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaS
 
 thread_local int g_hint_independent = 0;
 
-int exchange_wait_launch(const uint32_t *sync_local, int n_peers, cudaStream_t st) {
+int exchange_wait_launch(uint32_t *sync_local, int n_peers, cudaStream_t st) {
     exchange_wait_kernel<<<1, 32, 0, st>>>(sync_local, n_peers);
     T81_LAUNCH_CHECK("exchange_wait_kernel");
     return T81B200_OK;
