@@ -311,7 +311,7 @@ int launch_quantize_pack(const void *w, int64_t rows, int64_t cols, int64_t ld, 
     // rows that fit shared memory several times per SM: the row-in-shared-memory kernel
     const int64_t kl = (cols + 47) / 48;
     const size_t row_bytes = (size_t)((cols + 3) / 4) * 16 + (size_t)kl * 48;
-    if (row_bytes <= 64 * 1024) {
+    if (row_bytes <= 100 * 1024) {  // up to ~20 000 fp32 columns: at least two rows resident per SM
         auto rk = rule == T81B200_RULE_ABSMEAN ? quantize_pack_row_kernel<T, true> : quantize_pack_row_kernel<T, false>;
         if (row_bytes > 48 * 1024)
             T81_CUDA_TRY(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes));

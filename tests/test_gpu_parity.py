@@ -55,7 +55,7 @@ def test_pack_fixed_bit_exact_with_reference_fixtures(dev, golden):
 
 
 @pytest.mark.parametrize("rows,cols", [(1, 1), (3, 50), (64, 100), (7, 4096), (5, 4100), (3, 5000), (2, 16384),
-                                       (2, 20000), (300, 257)])
+                                       (2, 20000), (300, 257), (9, 14336), (2, 30000)])
 @pytest.mark.parametrize("rule", ["fixed", "absmean"])
 def test_pack_matches_oracle(dev, rows, cols, rule):
     from t81lib_b200 import ops
