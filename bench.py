@@ -352,7 +352,7 @@ def run_ours(args):
     bytes_decode = packed_bytes + sum(4 * m[1] + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
     gbs = bytes_decode * DECODE / (dec_ms * 1e-3) / 1e9
     gemv = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-            "kernel": "gemv_trit_kernel", "tokens": dtok, "cuda_graph": graph is not None,
+            "kernel": "gemv_trit_tma_kernel", "tokens": dtok, "cuda_graph": graph is not None,
             "note": "decode phase: 224 launches per step, includes launch gaps" + ("; whole on every rank" if world > 1 else "")}
 
     launches = args.steps * (1 + DECODE) * LAYERS * len(LINEARS)
@@ -493,7 +493,7 @@ def quantize_pack_line(torch, dev, ops, pk):
     sec = e0.elapsed_time(e1) * 1e-3 / (reps * len(ws))
     alg = 4096 * 4096 * 4 + 4096 * 86 * 16 + 4096 * 4
     return {"bound": "hbm", "achieved": alg / sec / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
-            "frac": alg / sec / 1e9 / pk["hbm_gbs"], "us_per_launch": sec * 1e6, "kernel": "quantize_pack_kernel"}
+            "frac": alg / sec / 1e9 / pk["hbm_gbs"], "us_per_launch": sec * 1e6, "kernel": "quantize_pack_row_kernel"}
 
 
 def run_kernel_case(args):
