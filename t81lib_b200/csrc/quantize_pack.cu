@@ -193,9 +193,7 @@ quantize_pack_row_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, in
     extern __shared__ __align__(16) uint8_t row_smem[];
     const int64_t kl = (cols + 47) / 48;
     const int64_t groups = (cols + 3) / 4;
-    const int64_t digit_words = kl * 12;
     float4 *rowf = reinterpret_cast<float4 *>(row_smem);                         // groups float4
-    uint32_t *digits = reinterpret_cast<uint32_t *>(row_smem + groups * 16);     // digit_words words
     __shared__ double group_sum[8];
     __shared__ float inv_shared;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -204,22 +202,23 @@ quantize_pack_row_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, in
         const T *row = w + r * ld;
         double part[2] = {0.0, 0.0};
         // m-th group of this thread: g = tid + 128 m; it belongs to partial g % 256 = tid + 128 (m % 2)
-        for (int64_t g0 = tid; g0 < groups; g0 += 8 * kRowThreads) {
+        const int ng = (int)groups;
+        for (int g0 = tid; g0 < ng; g0 += 8 * kRowThreads) {
             float v[8][4];  // eight loads in flight per thread before any is used
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int64_t g = g0 + kRowThreads * j;
-                if (g < groups) load_group<T>(row, 4 * g, cols, vec, v[j]);
+                const int g = g0 + kRowThreads * j;
+                if (g < ng) load_group<T>(row, 4 * (int64_t)g, cols, vec, v[j]);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int64_t g = g0 + kRowThreads * j;
-                if (g < groups) {
+                const int g = g0 + kRowThreads * j;
+                if (g < ng) {
                     rowf[g] = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
                     if constexpr (ABSMEAN) {
+                        // columns past the end were loaded as 0: adding |0| leaves a non-negative fp64 sum unchanged
 #pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            if (4 * g + c < cols) part[j & 1] += (double)fabsf(v[j][c]);
+                        for (int c = 0; c < 4; ++c) part[j & 1] += (double)fabsf(v[j][c]);
                     }
                 }
             }
@@ -248,33 +247,41 @@ quantize_pack_row_kernel(const T *__restrict__ w, int64_t rows, int64_t cols, in
             __syncthreads();
             inv = inv_shared;
         }
-        // digits: each thread re-reads the groups it wrote itself (no barrier needed for rowf)
-        for (int64_t g = tid; g < digit_words; g += kRowThreads) {
-            uint32_t word = 0x01010101u;
-            if (g < groups) {
-                const float4 f = rowf[g];
-                const float v[4] = {f.x, f.y, f.z, f.w};
-                word = 0;
+        if constexpr (!ABSMEAN) __syncthreads();  // the pack pass reads groups other threads loaded
+        // pack: one thread per output word = 4 trytes = 12 weights = groups 3q .. 3q+2 of the cached row.
+        // Digits are formed as floats (two compares each), a tryte is d0 + 3 d1 + 9 d2 (exact in fp32).
+        uint32_t *out = reinterpret_cast<uint32_t *>(packed + r * kl * 16);
+        const int nwords = (int)kl * 4;
+        const int ngroups = (int)groups, ncols = (int)cols;
+        for (int q = tid; q < nwords; q += kRowThreads) {
+            float d[12];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float x = ABSMEAN ? __fmul_rn(v[c], inv) : v[c];
-                    const uint32_t d = 4 * g + c < cols ? quantize_digit(x, thr) : 1u;
-                    word |= d << (8 * c);
+            for (int j = 0; j < 3; ++j) {
+                const int g = 3 * q + j;
+                if (g < ngroups) {
+                    const float4 f = rowf[g];
+                    const float v[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float x = ABSMEAN ? __fmul_rn(v[c], inv) : v[c];
+                        d[4 * j + c] = x <= -thr ? 0.0f : (x >= thr ? 2.0f : 1.0f);
+                    }
+                    if (4 * g + 4 > ncols) {  // the row's last, partial group: columns past the end are zero trits
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (4 * g + c >= ncols) d[4 * j + c] = 1.0f;
+                    }
+                } else {
+                    d[4 * j] = d[4 * j + 1] = d[4 * j + 2] = d[4 * j + 3] = 1.0f;  // padding up to the limb: zero trits
                 }
             }
-            digits[g] = word;
+            float y[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) y[t] = fmaf(9.0f, d[3 * t + 2], fmaf(3.0f, d[3 * t + 1], d[3 * t]));
+            const float low = fmaf(65536.0f, y[2], fmaf(256.0f, y[1], y[0]));  // < 2^24: exact
+            out[q] = (uint32_t)low + ((uint32_t)y[3] << 24);
         }
-        __syncthreads();
-        uint32_t *out = reinterpret_cast<uint32_t *>(packed + r * kl * 16);
-        for (int64_t q = tid; q < kl * 4; q += kRowThreads) {
-            const uint32_t a = digits[3 * q], b = digits[3 * q + 1], c = digits[3 * q + 2];
-            const uint32_t y0 = (a & 0xff) + 3u * ((a >> 8) & 0xff) + 9u * ((a >> 16) & 0xff);
-            const uint32_t y1 = (a >> 24) + 3u * (b & 0xff) + 9u * ((b >> 8) & 0xff);
-            const uint32_t y2 = ((b >> 16) & 0xff) + 3u * (b >> 24) + 9u * (c & 0xff);
-            const uint32_t y3 = ((c >> 8) & 0xff) + 3u * ((c >> 16) & 0xff) + 9u * (c >> 24);
-            out[q] = y0 | (y1 << 8) | (y2 << 16) | (y3 << 24);
-        }
-        __syncthreads();  // rowf / digits are reused by the next row
+        __syncthreads();  // the cached row is reused by the next row
     }
 }
 
@@ -309,9 +316,8 @@ int launch_quantize_pack(const void *w, int64_t rows, int64_t cols, int64_t ld, 
                          uint8_t *packed, float *row_scale, cudaStream_t st) {
     const bool vec = (reinterpret_cast<uintptr_t>(w) % (4 * sizeof(T)) == 0) && (ld % 4 == 0);
     // rows that fit shared memory several times per SM: the row-in-shared-memory kernel
-    const int64_t kl = (cols + 47) / 48;
-    const size_t row_bytes = (size_t)((cols + 3) / 4) * 16 + (size_t)kl * 48;
-    if (row_bytes <= 100 * 1024) {  // up to ~20 000 fp32 columns: at least two rows resident per SM
+    const size_t row_bytes = (size_t)((cols + 3) / 4) * 16;  // the row as fp32, whatever the input type
+    if (row_bytes <= 100 * 1024) {  // up to 25 600 columns: at least two rows resident per SM
         auto rk = rule == T81B200_RULE_ABSMEAN ? quantize_pack_row_kernel<T, true> : quantize_pack_row_kernel<T, false>;
         if (row_bytes > 48 * 1024)
             T81_CUDA_TRY(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes));
