@@ -186,16 +186,15 @@ class ShardedLinear(nn.Module):
         # of microseconds, a decode-sized matmul a few.  Needs the whole packed matrix on every
         # rank (2.67 bits per weight); the shard is then a view of it, not a second copy.
         self.shard_min_tokens = shard_min_tokens
-        # "collective": one all_gather_into_tensor per call (any backend).  "p2p": PeerColumns
-        # pushes over NVLink (CUDA, one node); the result is then a buffer owned by the module
-        # and reused two calls later.
+        # "collective": one all_gather_into_tensor per call (any backend).  "p2p": stores into the peers'
+        # results over NVLink (CUDA, one node); the result is then one of two shared buffers per shape and
+        # is reused two calls of that shape later.
         if exchange not in ("collective", "p2p"):
             raise ValueError(f"unknown exchange {exchange!r}")
         self.exchange = exchange
         # p2p only: True leaves the wait for the peers' blocks to the consumer — the next sharded matmul
         # waits at its start by itself; anything else calls ExchangeFlags.wait() first
         self.defer_wait = False
-        self._exchanges: dict = {}
         self._full_matmul = None
         self._full_bias = None if bias is None or shard_min_tokens <= 0 else bias.detach().clone()
         # `quantize` / `matmul` are injection points for host-side tests of the sharding
@@ -248,13 +247,22 @@ class ShardedLinear(nn.Module):
             return local
         return gather_columns(local, self.group)
 
+    # Result buffers are shared by every p2p layer of a process with the same (group, device, tokens, width,
+    # dtype): a stack of layers needs two buffers per width, not two per layer.  A result therefore stays
+    # valid until two more calls of that shape have been issued.
+    _shared_exchanges: dict = {}
+
+    def exchange_for(self, tokens: int, dtype: torch.dtype, device: torch.device) -> PeerColumns:
+        key = (id(self.group) if self.group is not None else None, device.index, tokens, self.out_features, dtype)
+        ex = ShardedLinear._shared_exchanges.get(key)
+        if ex is None:  # collective: every rank reaches this with the same shape
+            ex = ShardedLinear._shared_exchanges[key] = PeerColumns(tokens, self.out_features, dtype, device, self.group)
+        return ex
+
     def _forward_p2p(self, x: torch.Tensor) -> torch.Tensor:
         from .. import ops
         tokens = x.shape[0]
-        key = (tokens, x.dtype)
-        ex = self._exchanges.get(key)
-        if ex is None:  # collective: every rank reaches this with the same shape
-            ex = self._exchanges[key] = PeerColumns(tokens, self.out_features, x.dtype, x.device, self.group)
+        ex = self.exchange_for(tokens, x.dtype, x.device)
         i = ex.next_index()
         lo, hi = self.rows
         w = self.ternary_weight

@@ -45,7 +45,7 @@ def main() -> int:
     layer = ShardedLinear(w, b, threshold=0.45, rule="absmean", exchange="p2p")
     layer.defer_wait = True
     outs = [layer(x) for _ in range(40)]
-    layer._exchanges[(8, torch.bfloat16)].flags.wait()
+    layer.exchange_for(8, torch.bfloat16, dev).flags.wait()
     torch.cuda.synchronize()
     ok = ok and torch.equal(outs[-1], want) and torch.equal(outs[-2], want)
     ok = ok and _capi.kernel_status(reset=True) == 0
