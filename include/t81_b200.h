@@ -6,8 +6,8 @@
  *   - Plain C types only.  Every function returns T81B200_OK (0) or a negative
  *     T81B200_E* code; nothing throws, traps or aborts.  A description of the
  *     last failure on the calling thread is available from t81b200_last_error().
- *   - Unless a name ends in _host, every data pointer is a DEVICE pointer that
- *     the caller owns and lends for the duration of the call.  Work is queued on
+ *   - Unless a name ends in _host or _auto, every data pointer is a DEVICE pointer
+ *     that the caller owns and lends for the duration of the call.  Work is queued on
  *     `stream` (a cudaStream_t passed as void*; NULL = the legacy default
  *     stream) and the call returns without synchronising.
  *   - Nothing is allocated inside these calls, except where a comment says so;
@@ -147,7 +147,7 @@ T81B200_API int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, cons
 
 /* TRIT mode with HOST pointers, fp32 operands, KN layout (B is (K, N), C is (M, N), both
  * dense row-major) — the additive float-B overload of t81::linalg::gemm_ternary for C++
- * callers that hold std::span data (see INTEGRATION.md).  Copies in, runs, copies C back and
+ * callers that hold std::span data.  Copies in, runs, copies C back and
  * synchronises.  Allocates device staging buffers on first use and when sizes grow. */
 T81B200_API int t81b200_gemm_trit_host(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N,
                                        int64_t K, float alpha, float beta);
@@ -174,10 +174,43 @@ T81B200_API int t81b200_gemm_trit_static(const uint8_t *A, const float *row_scal
                                          int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta,
                                          void *stream);
 
+/* The two gemm_ternary forms for callers that hold a pointer without knowing where it
+ * lives — the slot of cuda_gemm_ternary (include/t81/linalg/gemm_gpu.hpp:122-129), which the
+ * dispatcher reaches with spans over host arrays (src/linalg/gemm_cuda.cu:284-341) and, through
+ * detail::gemm_ternary(const TensorMetadata&...) (src/linalg/gemm_dispatch.cpp:325-344), with
+ * spans over device memory when the metadata's device_type is CUDA.  A, B and C must all be
+ * host memory or all be memory of the current device.  Host operands are staged like the
+ * _host entry points; device operands are used in place on the legacy default stream.  Either
+ * way the call returns when C is complete (the reference synchronises for metadata with
+ * requires_sync, src/linalg/gemm_cuda.cu:205-209).  _limb_auto: LIMB mode, B packed limbs
+ * (k_limbs, N).  _trit_auto: TRIT mode, B fp32 (K, N), C (M, N). */
+T81B200_API int t81b200_gemm_limb_auto(const uint8_t *A, const uint8_t *B, float *C, int64_t M, int64_t N,
+                                       int64_t k_limbs, float alpha, float beta);
+T81B200_API int t81b200_gemm_trit_auto(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N,
+                                       int64_t K, float alpha, float beta);
+
+/* The four fp32 elementwise helpers of the reference's CUDA backend slot
+ * (cuda_where / cuda_clamp / cuda_lerp / cuda_addcmul, include/t81/linalg/gemm_gpu.hpp:75-78,217-231;
+ * kernels src/linalg/gemm_cuda.cu:165-283; CPU forms src/linalg/gemm_dispatch.cpp:147-222), over
+ * n contiguous floats, one IEEE operation per source operator (nothing fused):
+ *   WHERE    out = a != 0 ? b : c                    a condition, b x, c y
+ *   CLAMP    out = a < s0 ? s0 : (a > s1 ? s1 : a)   a input (b, c unused, may be NULL); s0 min, s1 max
+ *   LERP     out = a + c * (b - a)                   a start, b end, c weight
+ *   ADDCMUL  out = a + (s0 * b) * c                  a input, b tensor1, c tensor2; s0 value
+ * out may alias an input.  t81b200_elementwise takes device pointers and queues on `stream`;
+ * t81b200_elementwise_auto accepts host or device memory per pointer (host arrays are staged
+ * through device buffers that are allocated on first use and kept) and returns when out is complete. */
+enum { T81B200_EW_WHERE = 0, T81B200_EW_CLAMP = 1, T81B200_EW_LERP = 2, T81B200_EW_ADDCMUL = 3 };
+T81B200_API int t81b200_elementwise(int op, const float *a, const float *b, const float *c, float *out, int64_t n,
+                                    float s0, float s1, void *stream);
+T81B200_API int t81b200_elementwise_auto(int op, const float *a, const float *b, const float *c, float *out,
+                                         int64_t n, float s0, float s1);
+
 /* Status word of the tensor-core kernel on the current device: 0 = no problem seen;
  * 1..4 = a bounded wait inside the tensor-core kernel expired (producer, MMA issuer,
- * epilogue, converter), 5..6 = inside the streaming kernel (producer, consumer); that
- * launch's output is invalid.  The kernel never spins forever:
+ * epilogue, converter), 5..6 = inside the streaming kernel (producer, consumer), 7 = a wait
+ * on the exchange flags of a sharded call, 8 = the streaming kernel found dynamic shared memory
+ * starting above the address its tables were laid out for; that launch's output is invalid.  The kernel never spins forever:
  * every wait has an iteration limit after which it records the code, releases its
  * tensor memory and returns.  Reading the word synchronises the device; `reset`
  * non-zero clears it.  No counterpart in the reference (its CUDA path has no
@@ -238,6 +271,20 @@ T81B200_API void t81b200_hint_independent(int on);
  * (it has no multi-GPU path). */
 T81B200_API int t81b200_copy_columns(void *dst, int64_t dst_pitch, const void *src, int64_t src_pitch,
                          int64_t width_bytes, int64_t rows, void *stream);
+
+/* TRIT mode for up to T81B200_MAX_GROUP weight matrices that share their activations — the q, k and v
+ * projections of an attention block, or gate and up of an MLP: C[i] = alpha * diag(row_scale[i]) * T(A[i]) * B
+ * + bias[i] + beta * C[i], token-major (NK) layout, for i in [0, n_group).  A[i] is (M[i], ceil(K/48)) limbs;
+ * row_scale and bias are arrays of n_group pointers (the arrays or single entries may be NULL); every C[i] is
+ * (N, M[i]) with leading dimension ldc and dtype c_dtype.  With 1..16 tokens the whole group is ONE launch of the
+ * streaming kernel (a decode step issues 4 launches per decoder block instead of 7); larger token counts run
+ * one launch per matrix and then need bf16 activations (there is no workspace argument).
+ * No counterpart in the reference, whose nn.Linear modules are called one by one (t81/nn/linear.py:53-70). */
+#define T81B200_MAX_GROUP 3
+T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, const float *const *row_scale,
+                                          const float *const *bias, void *const *C, const int64_t *M, const void *B,
+                                          int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
+                                          float alpha, float beta, void *stream);
 
 T81B200_API size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int c_dtype, int64_t M,
                                          int64_t N, int64_t K);

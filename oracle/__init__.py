@@ -167,3 +167,30 @@ def linear_forward(W_packed, row_scale, bias, x, in_features: int) -> np.ndarray
     lib().t81o_linear_forward(_ptr(W), _ptr(rs), _ptr(b), _ptr(x), _ptr(y), x.shape[0],
                               out_features, in_features)
     return y
+
+
+# ---- the four elementwise helpers next to the GEMM in the reference's backend slot ----------------
+# src/linalg/gemm_dispatch.cpp:147-222 (cpu_where / cpu_clamp / cpu_lerp / cpu_addcmul): float32
+# arrays of equal length, one IEEE float32 operation per source operator (numpy float32 arithmetic
+# rounds after every operation, like that code compiled without contraction).
+
+
+def where(condition, x, y) -> np.ndarray:
+    c, x, y = _f32c(condition), _f32c(x), _f32c(y)
+    return np.where(c != np.float32(0.0), x, y).astype(np.float32)
+
+
+def clamp(values, min_value: float, max_value: float) -> np.ndarray:
+    v = _f32c(values)
+    lo, hi = np.float32(min_value), np.float32(max_value)
+    return np.where(v < lo, lo, np.where(v > hi, hi, v)).astype(np.float32)
+
+
+def lerp(start, end, weight) -> np.ndarray:
+    s, e, w = _f32c(start), _f32c(end), _f32c(weight)
+    return (s + w * (e - s)).astype(np.float32)
+
+
+def addcmul(input, tensor1, tensor2, value: float = 1.0) -> np.ndarray:
+    a, t1, t2 = _f32c(input), _f32c(tensor1), _f32c(tensor2)
+    return (a + (np.float32(value) * t1) * t2).astype(np.float32)

@@ -53,3 +53,22 @@ def load():
         spec.loader.exec_module(mod)
         _mod = mod
     return _mod
+
+
+def cuda_dir() -> str:
+    """Where ``make -C oracle ref_cuda`` puts the reference built with its CUDA backend slot filled
+    by this repository's shim (``t81lib`` module and ``ref_cuda_driver``)."""
+    return os.path.join(_HERE, "_ref", "cuda")
+
+
+def load_cuda():
+    """Import the reference's ``t81lib`` module built with T81LIB_USE_CUDA=1 against the shim."""
+    p = os.path.join(cuda_dir(), "t81lib" + sysconfig.get_config_var("EXT_SUFFIX"))
+    if not os.path.exists(p):
+        raise FileNotFoundError(f"{p} missing: run `make -C oracle ref_cuda` where the reference is mounted")
+    spec = importlib.util.spec_from_file_location("t81lib_cuda_build", p)
+    # the extension's init function is PyInit_t81lib whatever name it is loaded under
+    spec = importlib.util.spec_from_file_location("t81lib", p)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod

@@ -26,7 +26,11 @@ EXPORTS = (
     "t81b200_quantize_trits", "t81b200_unpack", "t81b200_gemm_limb", "t81b200_gemm_limb_host",
     "t81b200_gemm_trit", "t81b200_gemm_trit_host", "t81b200_gemm_trit_static", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
     "t81b200_copy_columns", "t81b200_gemm_trit_peers", "t81b200_exchange_wait", "t81b200_hint_independent",
+    "t81b200_gemm_limb_auto", "t81b200_gemm_trit_auto", "t81b200_elementwise", "t81b200_elementwise_auto",
+    "t81b200_gemm_trit_grouped",
 )
+MAX_GROUP = 3       # T81B200_MAX_GROUP
+EW_WHERE, EW_CLAMP, EW_LERP, EW_ADDCMUL = 0, 1, 2, 3
 
 
 class T81B200Error(RuntimeError):
@@ -69,6 +73,13 @@ def _load() -> ctypes.CDLL:
                                             vp, ctypes.c_size_t, ci, ctypes.POINTER(vp), vp, ctypes.POINTER(vp), vp]
     lib.t81b200_exchange_wait.argtypes = [vp, ci, vp]
     lib.t81b200_hint_independent.argtypes = [ci]
+    lib.t81b200_gemm_limb_auto.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32]
+    lib.t81b200_gemm_trit_auto.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32]
+    lib.t81b200_elementwise.argtypes = [ci, vp, vp, vp, vp, i64, f32, f32, vp]
+    lib.t81b200_elementwise_auto.argtypes = [ci, vp, vp, vp, vp, i64, f32, f32]
+    lib.t81b200_gemm_trit_grouped.argtypes = [ci, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp),
+                                              ctypes.POINTER(vp), ctypes.POINTER(i64), vp, ci, i64, ci, i64, i64, i64,
+                                              f32, f32, vp]
     lib.t81b200_hint_independent.restype = None
     for name in EXPORTS:
         fn = getattr(lib, name)

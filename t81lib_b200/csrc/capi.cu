@@ -1,7 +1,6 @@
 // C ABI glue: error state, device probing and the TRIT-mode dispatcher.
 #include "common.cuh"
 
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -83,6 +82,10 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
 
 int gemm_trit_tc_status(int reset);
 int gemv_trit_status(int reset);
+int gemv_trit_lut_status(int reset);
+int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
+                         void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
+                         int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx);
 
 }  // namespace t81b200
 
@@ -92,7 +95,8 @@ extern "C" int t81b200_kernel_status(int reset) {
     if (int rc = check_device()) return rc;
     const int tc = gemm_trit_tc_status(reset);
     const int gv = gemv_trit_status(reset);
-    return tc != 0 ? tc : gv;
+    const int lut = gemv_trit_lut_status(reset);
+    return tc != 0 ? tc : (gv != 0 ? gv : lut);
 }
 
 extern "C" int t81b200_copy_columns(void *dst, int64_t dst_pitch, const void *src, int64_t src_pitch,
@@ -209,10 +213,7 @@ static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool a_aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0;
 
-    // T81B200_SMALLN_PATH=tc sends token counts <= 16 to the tensor-core kernel too (A/B runs).
-    const char *small_n = getenv("T81B200_SMALLN_PATH");
-    const bool small_n_tc = small_n && small_n[0] == 't' && b_dtype == T81B200_BF16;
-    if (a_aligned && layout == T81B200_LAYOUT_NK && N <= 16 && K > 0 && !small_n_tc)
+    if (a_aligned && layout == T81B200_LAYOUT_NK && N <= 16 && K > 0)
         return gemv_trit_launch(A, row_scale, B, b_dtype, ldb, bias, C, c_dtype, ldc, M, (int)N, K, alpha, beta, st, ctx);
 
     // the other kernels do not carry the exchange protocol: wait for the peers' stores before they read
@@ -234,4 +235,38 @@ static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void 
         }
     }
     return gemm_trit_simt_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, st);
+}
+
+extern "C" int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, const float *const *row_scale,
+                                         const float *const *bias, void *const *C, const int64_t *M, const void *B,
+                                         int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
+                                         float alpha, float beta, void *stream) {
+    if (n_group < 1 || n_group > T81B200_MAX_GROUP)
+        return fail(T81B200_ELIMIT, "gemm_trit_grouped: %d matrices, between 1 and %d are supported", n_group, T81B200_MAX_GROUP);
+    if (!A || !C || !M) return fail(T81B200_EINVAL, "gemm_trit_grouped: null pointer");
+    if (N < 0 || K < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
+    if (!valid_dtype(b_dtype) || !valid_dtype(c_dtype)) return fail(T81B200_EINVAL, "gemm_trit: unknown dtype");
+    if (ldb < K) return fail(T81B200_EINVAL, "gemm_trit: ldb (%lld) below the row length (%lld)", (long long)ldb, (long long)K);
+    bool streaming = N >= 1 && N <= 16 && K > 0;
+    for (int i = 0; i < n_group; ++i) {
+        if (M[i] < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
+        if (ldc < M[i]) return fail(T81B200_EINVAL, "gemm_trit: ldc (%lld) below the row length (%lld)", (long long)ldc, (long long)M[i]);
+        if (M[i] > 0 && N > 0 && (!C[i] || (K > 0 && (!A[i] || !B)))) return fail(T81B200_EINVAL, "gemm_trit: null pointer");
+        streaming = streaming && M[i] > 0 && reinterpret_cast<uintptr_t>(A[i]) % 16 == 0;
+    }
+    if (int rc = check_device()) return rc;
+    if (N == 0) return T81B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (streaming) {
+        const int rc = gemv_trit_lut_launch(n_group, A, row_scale, bias, C, M, B, b_dtype, ldb, c_dtype, ldc, (int)N, K, alpha,
+                                            beta, st, nullptr);
+        if (rc != T81B200_EALIGN) return rc;
+    }
+    // anything else: one call per matrix
+    for (int i = 0; i < n_group; ++i)
+        if (int rc = gemm_trit_local(A[i], row_scale ? row_scale[i] : nullptr, B, b_dtype, T81B200_LAYOUT_NK, ldb,
+                                     bias ? bias[i] : nullptr, C[i], c_dtype, ldc, M[i], N, K, alpha, beta, nullptr, 0, stream,
+                                     nullptr))
+            return rc;
+    return T81B200_OK;
 }

@@ -32,6 +32,8 @@ int exchange_wait_launch(uint32_t *sync_local, int n_peers, cudaStream_t st);
 int exchange_signal_launch(uint32_t *sync_local, uint32_t *const *slots, int n_peers, cudaStream_t st);
 
 int sm_count();      // multiprocessors of the current device (cached per device)
+// *is_device = 1 when a kernel of the current device can dereference p (device or managed memory), 0 for host memory
+int pointer_is_device(const void *p, int *is_device);
 
 #define T81_CUDA_TRY(expr)                                                              \
     do {                                                                                \

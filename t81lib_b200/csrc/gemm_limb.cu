@@ -68,13 +68,23 @@ gemm_limb_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, f
     if (live) C[i * N + j] = (float)acc;
 }
 
+// Staging buffers of the entry points that take host pointers: one set per device, kept for
+// the life of the process and grown on demand.
 struct HostStaging {
     std::mutex mu;
     void *a = nullptr, *b = nullptr, *c = nullptr, *ws = nullptr;
     size_t a_cap = 0, b_cap = 0, c_cap = 0, ws_cap = 0;
-    int device = -1;
 };
-HostStaging g_staging;
+constexpr int kMaxDevices = 64;
+HostStaging g_staging[kMaxDevices];
+
+int staging_for_current_device(HostStaging **out) {
+    int dev = 0;
+    T81_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(T81B200_ELIMIT, "device index %d not supported", dev);
+    *out = &g_staging[dev];
+    return T81B200_OK;
+}
 
 int grow(void **p, size_t *cap, size_t need) {
     if (need <= *cap) return T81B200_OK;
@@ -86,6 +96,22 @@ int grow(void **p, size_t *cap, size_t need) {
 }
 
 }  // namespace
+
+// 1: memory a kernel of the current device can dereference (device or managed memory);
+// 0: host memory (pageable or pinned).  Null pointers count as "either".
+int pointer_is_device(const void *p, int *is_device) {
+    *is_device = 0;
+    if (!p) return T81B200_OK;
+    cudaPointerAttributes attr;
+    const cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();  // older runtimes report plain host memory as an error
+        return T81B200_OK;
+    }
+    *is_device = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    return T81B200_OK;
+}
+
 }  // namespace t81b200
 
 using namespace t81b200;
@@ -109,26 +135,61 @@ extern "C" int t81b200_gemm_limb_host(const uint8_t *A, const uint8_t *B, float 
     if (int rc = check_device()) return rc;
     if (M == 0 || N == 0) return T81B200_OK;
     if (!C || (k_limbs > 0 && (!A || !B))) return fail(T81B200_EINVAL, "gemm_limb_host: null pointer");
-    std::lock_guard<std::mutex> lock(g_staging.mu);
-    int dev = 0;
-    T81_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev != g_staging.device) {
-        // buffers belong to the device they were allocated on
-        g_staging.a = g_staging.b = g_staging.c = g_staging.ws = nullptr;
-        g_staging.a_cap = g_staging.b_cap = g_staging.c_cap = g_staging.ws_cap = 0;
-        g_staging.device = dev;
-    }
+    HostStaging *stg = nullptr;
+    if (int rc = staging_for_current_device(&stg)) return rc;
+    std::lock_guard<std::mutex> lock(stg->mu);
     const size_t a_bytes = (size_t)M * k_limbs * 16, b_bytes = (size_t)k_limbs * N * 16, c_bytes = (size_t)M * N * 4;
-    if (int rc = grow(&g_staging.a, &g_staging.a_cap, a_bytes ? a_bytes : 16)) return rc;
-    if (int rc = grow(&g_staging.b, &g_staging.b_cap, b_bytes ? b_bytes : 16)) return rc;
-    if (int rc = grow(&g_staging.c, &g_staging.c_cap, c_bytes)) return rc;
-    if (a_bytes) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.a, A, a_bytes, cudaMemcpyHostToDevice, 0));
-    if (b_bytes) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.b, B, b_bytes, cudaMemcpyHostToDevice, 0));
-    T81_CUDA_TRY(cudaMemcpyAsync(g_staging.c, C, c_bytes, cudaMemcpyHostToDevice, 0));
-    if (int rc = t81b200_gemm_limb((const uint8_t *)g_staging.a, (const uint8_t *)g_staging.b, (float *)g_staging.c,
+    if (int rc = grow(&stg->a, &stg->a_cap, a_bytes ? a_bytes : 16)) return rc;
+    if (int rc = grow(&stg->b, &stg->b_cap, b_bytes ? b_bytes : 16)) return rc;
+    if (int rc = grow(&stg->c, &stg->c_cap, c_bytes)) return rc;
+    if (a_bytes) T81_CUDA_TRY(cudaMemcpyAsync(stg->a, A, a_bytes, cudaMemcpyHostToDevice, 0));
+    if (b_bytes) T81_CUDA_TRY(cudaMemcpyAsync(stg->b, B, b_bytes, cudaMemcpyHostToDevice, 0));
+    T81_CUDA_TRY(cudaMemcpyAsync(stg->c, C, c_bytes, cudaMemcpyHostToDevice, 0));
+    if (int rc = t81b200_gemm_limb((const uint8_t *)stg->a, (const uint8_t *)stg->b, (float *)stg->c,
                                    M, N, k_limbs, alpha, beta, nullptr))
         return rc;
-    T81_CUDA_TRY(cudaMemcpyAsync(C, g_staging.c, c_bytes, cudaMemcpyDeviceToHost, 0));
+    T81_CUDA_TRY(cudaMemcpyAsync(C, stg->c, c_bytes, cudaMemcpyDeviceToHost, 0));
+    T81_CUDA_TRY(cudaStreamSynchronize(0));
+    return T81B200_OK;
+}
+
+extern "C" int t81b200_gemm_limb_auto(const uint8_t *A, const uint8_t *B, float *C, int64_t M, int64_t N,
+                                      int64_t k_limbs, float alpha, float beta) {
+    if (M < 0 || N < 0 || k_limbs < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
+    if (int rc = check_device()) return rc;
+    if (M == 0 || N == 0) return T81B200_OK;
+    int da = 0, db = 0, dc = 0;
+    pointer_is_device(A, &da); pointer_is_device(B, &db); pointer_is_device(C, &dc);
+    if (k_limbs == 0) da = db = dc;
+    if (da != dc || db != dc)
+        return fail(T81B200_EINVAL, "gemm_ternary: A, B and C must all be host memory or all be device memory");
+    if (!dc) return t81b200_gemm_limb_host(A, B, C, M, N, k_limbs, alpha, beta);
+    // device-resident operands (TensorMetadata with device_type CUDA and requires_sync): run in place on
+    // the legacy default stream and return when the result is complete
+    if (int rc = t81b200_gemm_limb(A, B, C, M, N, k_limbs, alpha, beta, nullptr)) return rc;
+    T81_CUDA_TRY(cudaStreamSynchronize(0));
+    return T81B200_OK;
+}
+
+static int gemm_trit_host_impl(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N, int64_t K,
+                               float alpha, float beta) {
+    HostStaging *stg = nullptr;
+    if (int rc = staging_for_current_device(&stg)) return rc;
+    std::lock_guard<std::mutex> lock(stg->mu);
+    const int64_t kl = (K + 47) / 48;
+    const size_t a_bytes = (size_t)M * kl * 16, b_bytes = (size_t)K * N * 4, c_bytes = (size_t)M * N * 4;
+    const size_t ws_bytes = t81b200_gemm_trit_workspace_bytes(T81B200_F32, T81B200_LAYOUT_KN, T81B200_F32, M, N, K);
+    if (int rc = grow(&stg->a, &stg->a_cap, a_bytes ? a_bytes : 16)) return rc;
+    if (int rc = grow(&stg->b, &stg->b_cap, b_bytes ? b_bytes : 16)) return rc;
+    if (int rc = grow(&stg->c, &stg->c_cap, c_bytes)) return rc;
+    if (ws_bytes) if (int rc = grow(&stg->ws, &stg->ws_cap, ws_bytes)) return rc;
+    if (a_bytes) T81_CUDA_TRY(cudaMemcpyAsync(stg->a, A, a_bytes, cudaMemcpyHostToDevice, 0));
+    if (b_bytes) T81_CUDA_TRY(cudaMemcpyAsync(stg->b, B, b_bytes, cudaMemcpyHostToDevice, 0));
+    if (beta != 0.0f) T81_CUDA_TRY(cudaMemcpyAsync(stg->c, C, c_bytes, cudaMemcpyHostToDevice, 0));
+    if (int rc = t81b200_gemm_trit((const uint8_t *)stg->a, nullptr, stg->b, T81B200_F32, T81B200_LAYOUT_KN, N,
+                                   nullptr, stg->c, T81B200_F32, N, M, N, K, alpha, beta, stg->ws, stg->ws_cap, nullptr))
+        return rc;
+    T81_CUDA_TRY(cudaMemcpyAsync(C, stg->c, c_bytes, cudaMemcpyDeviceToHost, 0));
     T81_CUDA_TRY(cudaStreamSynchronize(0));
     return T81B200_OK;
 }
@@ -139,29 +200,29 @@ extern "C" int t81b200_gemm_trit_host(const uint8_t *A, const float *B, float *C
     if (int rc = check_device()) return rc;
     if (M == 0 || N == 0) return T81B200_OK;
     if (!C || (K > 0 && (!A || !B))) return fail(T81B200_EINVAL, "gemm_trit_host: null pointer");
-    std::lock_guard<std::mutex> lock(g_staging.mu);
-    int dev = 0;
-    T81_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev != g_staging.device) {
-        g_staging.a = g_staging.b = g_staging.c = g_staging.ws = nullptr;
-        g_staging.a_cap = g_staging.b_cap = g_staging.c_cap = g_staging.ws_cap = 0;
-        g_staging.device = dev;
-    }
-    const int64_t kl = (K + 47) / 48;
-    const size_t a_bytes = (size_t)M * kl * 16, b_bytes = (size_t)K * N * 4, c_bytes = (size_t)M * N * 4;
+    return gemm_trit_host_impl(A, B, C, M, N, K, alpha, beta);
+}
+
+extern "C" int t81b200_gemm_trit_auto(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N, int64_t K,
+                                      float alpha, float beta) {
+    if (M < 0 || N < 0 || K < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
+    if (int rc = check_device()) return rc;
+    if (M == 0 || N == 0) return T81B200_OK;
+    if (!C || (K > 0 && (!A || !B))) return fail(T81B200_EINVAL, "gemm_trit: null pointer");
+    int da = 0, db = 0, dc = 0;
+    pointer_is_device(A, &da); pointer_is_device(B, &db); pointer_is_device(C, &dc);
+    if (K == 0) da = db = dc;
+    if (da != dc || db != dc)
+        return fail(T81B200_EINVAL, "gemm_ternary: A, B and C must all be host memory or all be device memory");
+    if (!dc) return gemm_trit_host_impl(A, B, C, M, N, K, alpha, beta);
+    HostStaging *stg = nullptr;
+    if (int rc = staging_for_current_device(&stg)) return rc;
+    std::lock_guard<std::mutex> lock(stg->mu);
     const size_t ws_bytes = t81b200_gemm_trit_workspace_bytes(T81B200_F32, T81B200_LAYOUT_KN, T81B200_F32, M, N, K);
-    if (int rc = grow(&g_staging.a, &g_staging.a_cap, a_bytes ? a_bytes : 16)) return rc;
-    if (int rc = grow(&g_staging.b, &g_staging.b_cap, b_bytes ? b_bytes : 16)) return rc;
-    if (int rc = grow(&g_staging.c, &g_staging.c_cap, c_bytes)) return rc;
-    if (ws_bytes) if (int rc = grow(&g_staging.ws, &g_staging.ws_cap, ws_bytes)) return rc;
-    if (a_bytes) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.a, A, a_bytes, cudaMemcpyHostToDevice, 0));
-    if (b_bytes) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.b, B, b_bytes, cudaMemcpyHostToDevice, 0));
-    if (beta != 0.0f) T81_CUDA_TRY(cudaMemcpyAsync(g_staging.c, C, c_bytes, cudaMemcpyHostToDevice, 0));
-    if (int rc = t81b200_gemm_trit((const uint8_t *)g_staging.a, nullptr, g_staging.b, T81B200_F32, T81B200_LAYOUT_KN, N,
-                                   nullptr, g_staging.c, T81B200_F32, N, M, N, K, alpha, beta, g_staging.ws,
-                                   g_staging.ws_cap, nullptr))
+    if (ws_bytes) if (int rc = grow(&stg->ws, &stg->ws_cap, ws_bytes)) return rc;
+    if (int rc = t81b200_gemm_trit(A, nullptr, B, T81B200_F32, T81B200_LAYOUT_KN, N, nullptr, C, T81B200_F32, N, M, N, K,
+                                   alpha, beta, stg->ws, stg->ws_cap, nullptr))
         return rc;
-    T81_CUDA_TRY(cudaMemcpyAsync(C, g_staging.c, c_bytes, cudaMemcpyDeviceToHost, 0));
     T81_CUDA_TRY(cudaStreamSynchronize(0));
     return T81B200_OK;
 }

@@ -22,7 +22,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 
-#include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -126,6 +126,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
 }
 
+
+// AND of a predicate over the 128 epilogue threads (named barrier 2); every one of them must call it.
+__device__ __forceinline__ bool epilogue_all(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "barrier.cta.red.and.pred p, 2, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
 
 // PLANES = 1: bf16 activations as they are.  PLANES = 2: activations split into a bf16 "hi"
 // plane and a bf16 "lo" plane (x = hi + lo to 16 mantissa bits); both are multiplied with the
@@ -252,7 +266,9 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * BN;
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), acc_phase));  // warp-uniform: tcgen05.ld is .aligned
+            // One decision for all four epilogue warps (tcgen05.ld is .aligned, and the staging path below
+            // meets at named barriers): every thread's bounded wait returns, then the 128 threads agree.
+            ok = epilogue_all(mbar_wait(acc_full(buf), acc_phase));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int64_t row = (int64_t)m0 + lane_group * 32 + lane;
@@ -405,14 +421,16 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 template <typename CT, int PLANES>
 int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcOutMaps &om, const TcParams &p, cudaStream_t st) {
     auto kern = gemm_trit_tc_kernel<CT, PLANES>;
-    static bool configured = false;
-    if (!configured) {
+    // the shared-memory limit is a per-device attribute of the function: set it once on every device
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    T81_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     const int tiles = p.m_tiles * p.n_tiles;
-    int sms = sm_count();
-    if (const char *env = getenv("T81B200_TC_SM_RESERVE")) { const int r = atoi(env); if (r > 0 && r < sms) sms -= r; }
+    const int sms = sm_count();
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(mw, mx, om, p);
     T81_LAUNCH_CHECK("gemm_trit_tc_kernel");
@@ -578,7 +596,7 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
     p.n_out_maps = 0;
     const size_t esz = dtype_size(c_dtype);
     bool tma_out = esz == 2 && layout == T81B200_LAYOUT_NK && beta == 0.0f && (ldc * 2) % 16 == 0 &&
-                   reinterpret_cast<uintptr_t>(C) % 16 == 0 && !(getenv("T81B200_TC_EPILOGUE") && getenv("T81B200_TC_EPILOGUE")[0] == 'd');
+                   reinterpret_cast<uintptr_t>(C) % 16 == 0;
     for (int i = 0; i < n_peers; ++i) tma_out = tma_out && reinterpret_cast<uintptr_t>(peer_C[i]) % 16 == 0;
     if (tma_out) {
         const CUtensorMapDataType dt = c_dtype == T81B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

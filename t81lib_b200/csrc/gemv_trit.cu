@@ -19,6 +19,7 @@
 //   shared memory already permuted into the register order decode_limb produces.
 #include "common.cuh"
 #include "tma.cuh"
+#include "exchange.cuh"
 
 #include <cooperative_groups.h>
 
@@ -47,57 +48,6 @@ struct GemvParams {
     int n_peers;            // other GPUs whose result receives every output element too
     void *peer_C[T81B200_MAX_PEERS];
 };
-
-// ---- exchange flags of the column-sharded Linear ----------------------------------------------
-// sync_local (this GPU's memory, T81B200_SYNC_WORDS words, zero at start):
-//   [0] CTAs of the running kernel that have finished storing   [1] exchanges this rank has completed
-//   [2] non-zero once a wait has expired on this rank
-//   [16 * (1 + j)] the sequence number peer j has published here
-// A kernel that stores into the peers ends with exchange_signal (the last CTA publishes the new
-// sequence number into each peer's slot); a kernel that reads what the peers stored starts with
-// exchange_wait.  Every wait is bounded.
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ bool exchange_wait(uint32_t *sync_local, int n_peers) {
-    const uint32_t expected = *reinterpret_cast<const volatile uint32_t *>(sync_local + 1);
-    // [2]: a wait on this rank has expired before (a peer is gone or out of step).  Later waits give up at
-    // once, so a lost peer costs one time limit (a few seconds), not one per call.
-    if (*reinterpret_cast<const volatile uint32_t *>(sync_local + 2) != 0u) return false;
-    for (int j = 0; j < n_peers; ++j) {
-        const uint32_t *flag = sync_local + 16 * (1 + j);
-        bool seen = false;
-        for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
-            if ((int32_t)(ld_acquire_sys(flag) - expected) >= 0) { seen = true; break; }
-            if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
-        }
-        if (!seen) {
-            *reinterpret_cast<volatile uint32_t *>(sync_local + 2) = 1u;
-            return false;
-        }
-    }
-    return true;
-}
-
-// Called by one thread per CTA after the CTA's stores and a CTA barrier.
-__device__ __forceinline__ void exchange_signal(uint32_t *sync_local, uint32_t *const *sync_peer, int n_peers,
-                                                uint32_t total_ctas) {
-    __threadfence_system();
-    const uint32_t old = atomicAdd(sync_local, 1u);
-    if (old == total_ctas - 1) {
-        *reinterpret_cast<volatile uint32_t *>(sync_local) = 0u;
-        const uint32_t seq = *reinterpret_cast<volatile uint32_t *>(sync_local + 1) + 1u;
-        *reinterpret_cast<volatile uint32_t *>(sync_local + 1) = seq;
-        __threadfence_system();
-        for (int j = 0; j < n_peers; ++j) st_release_sys(sync_peer[j], seq);
-    }
-}
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -710,8 +660,7 @@ int gemv_trit_tma_launch(const GemvParams &base, int x_dtype, int c_dtype, cudaS
     const size_t budget = 200 * 1024;
     int best_rw = 0, best_s = 1, best_lps = 4, best_stages = 0;
     double best_t = 1e30;
-    int forced_rw = 0, forced_s = 0, forced_kw = 0;  // T81B200_GEMV_TMA_CFG="row_warps,slices[,k_warps]" (sweeps)
-    if (const char *env = getenv("T81B200_GEMV_TMA_CFG")) sscanf(env, "%d,%d,%d", &forced_rw, &forced_s, &forced_kw);
+    const int forced_rw = 0, forced_s = 0, forced_kw = 0;
     int best_kw = 1;
     for (int rwv = 1; rwv <= kTmaMaxConsumerWarps; ++rwv)
         for (int kwv = 1; rwv * kwv <= kTmaMaxConsumerWarps; ++kwv)
@@ -804,6 +753,10 @@ int gemv_trit_status(int reset) {
 namespace {
 }  // namespace
 
+int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
+                         void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
+                         int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx);
+
 // Host entry used by the dispatcher in capi.cu.  NK layout, ntok in 1..16, A 16-byte aligned.
 int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, int x_dtype, int64_t ldx,
                      const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int ntok, int64_t K,
@@ -819,9 +772,18 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     const int tokpad = ntok > 8 ? 16 : 8;
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
 
-    // Default: the TMA-fed kernel.  T81B200_GEMV_PATH=ldg selects the register-prefetch kernel (A/B runs).
-    const char *path = getenv("T81B200_GEMV_PATH");
-    if (!(path && path[0] == 'l')) {
+    // Default: the table-decode kernel.  T81B200_GEMV_PATH (read once per process; A/B runs) selects an older
+    // kernel instead: "fma" the TMA-fed kernel with arithmetic decode, "ldg" the register-prefetch kernel.
+    static const char path = [] { const char *e = getenv("T81B200_GEMV_PATH"); return e ? e[0] : '\0'; }();
+    if (path == '\0') {
+        const float *rs = row_scale, *bs = bias;
+        void *cc = C;
+        const int rc = gemv_trit_lut_launch(1, &A, &rs, &bs, &cc, &M, X, x_dtype, ldx, c_dtype, ldc, ntok, K, alpha, beta, st, ctx);
+        if (rc != T81B200_EALIGN) {
+            if (ctx && ctx->sync_local && rc == T81B200_OK) ctx->sync_fused = true;
+            return rc;
+        }
+    } else if (path == 'f') {
         p.row_warps = 1; p.row_groups = 1; p.limbs_per_slice = 4;
         const int rc = gemv_trit_tma_launch(p, x_dtype, c_dtype, st, ctx);
         if (rc != T81B200_EALIGN) {
@@ -869,19 +831,6 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
                 }
     if (best_t >= 1e30)
         return fail(T81B200_ELIMIT, "gemm_trit: K=%lld too large for the streaming kernel", (long long)K);
-    // Tuning override: T81B200_GEMV_CFG="warps,row_warps,row_groups,slices" (used by sweeps; unset in production).
-    if (const char *env = getenv("T81B200_GEMV_CFG")) {
-        int w = 0, rwv = 0, rg = 0, sl = 0;
-        if (sscanf(env, "%d,%d,%d,%d,%d", &w, &rwv, &rg, &sl, &variant) >= 4 && (w == 8 || w == 16) && rwv >= 1 && rwv <= w &&
-            (rwv & (rwv - 1)) == 0 && rg >= 1 && rg <= 64 && sl >= 1 && sl <= 8) {
-            int lps = (kl4 / 4 + sl - 1) / sl * 4;
-            if (lps < 4) lps = 4;
-            const size_t need = gemv_smem_bytes(planes, ntok, tokpad, lps, w, rwv, rg);
-            if (!(sl > 1 && (int64_t)(sl - 1) * lps >= kl4) && need <= 200 * 1024) {
-                best_w = w; best_rw = rwv; best_rg = rg; best_s = sl; best_lps = lps;
-            }
-        }
-    }
     p.row_warps = best_rw;
     p.row_groups = best_rg;
     p.limbs_per_slice = best_lps;

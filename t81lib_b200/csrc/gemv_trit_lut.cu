@@ -1,0 +1,666 @@
+// Decode-shaped TRIT-mode kernel, table-decode form: packed ternary weights (M rows) times up to 16
+// activation rows (tokens), HBM-bound by design.
+//
+// Pipeline of one CTA (up to 16 consumer warps + 1 producer warp):
+//   * the producer thread streams the CTA's weight rows through a shared-memory ring with TMA
+//     (stages of 32*RW rows x 64 bytes = one 4-limb chunk per row); nothing in that stream depends
+//     on the previous kernel of the stream, so it starts before the programmatic-dependent-launch wait;
+//   * the activations arrive with one bulk copy per token (cp.async.bulk, no per-thread round trips)
+//     after that wait, in their natural order;
+//   * consumer warp (rw, kw) takes chunks kw, kw + KW, ... of rows 32*rw .. 32*rw+31: lane (g, t) reads
+//     limb t of rows g, g+8, g+16, g+24 with 128-bit shared loads and expands every tryte byte with ONE
+//     shared-memory table look-up into exact bf16 {-1,0,+1}: the byte is dropped into bits 8..15 of the
+//     look-up address by a single PRMT; the table holds, per byte value, a copy for each of 16 lanes
+//     (256 bytes per value), so the 64-bit loads of a warp never meet on a bank whatever the bytes are.
+//     Two tables (bytes at even / odd positions) place the three trits so that one OR per byte pair
+//     gives registers holding adjacent trits: the A fragments of mma.sync m16n8k16 in natural
+//     contraction order, which is why the activations need no re-ordering.  The same activation
+//     fragments serve both 16-row groups of the warp.
+//   * fp32 accumulation in registers; the K-slices of a CTA meet in shared memory, the K-slices of a
+//     cluster (shapes with few rows) through distributed shared memory in rank order: deterministic,
+//     no global scratch, no atomics.  Row scales and biases are fetched into shared memory at the start.
+//
+// Up to three weight matrices that share their activations (q/k/v, gate/up) can be served by one launch:
+// row tiles are numbered through the segments.
+//
+// Bytes above 26 are not valid trytes (the packer never writes them; limb::from_bytes of the reference
+// rejects them, include/t81/core/limb.hpp:160-169).  Here they index past the 27 table entries into other
+// shared memory of the CTA: the affected outputs are unspecified, and the launch keeps its allocation
+// large enough that no such read can leave it.
+#include "common.cuh"
+#include "tma.cuh"
+#include "exchange.cuh"
+
+#include <cooperative_groups.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+namespace cg = cooperative_groups;
+
+namespace t81b200 {
+
+namespace {
+
+constexpr int kMaxSeg = T81B200_MAX_GROUP;
+constexpr int kMaxConsumerWarps = 16;
+constexpr int kThreads = (kMaxConsumerWarps + 1) * 32;
+constexpr int kMaxStages = 48;
+// The tables sit at this absolute shared-memory address: its bits 8..15 are zero, so a look-up address is
+// this constant with the byte value dropped into byte 1 and the lane offset into byte 0.
+constexpr uint32_t kLutAbs = 0x10000u;
+constexpr int kLutBytes = 27 * 256;
+// Dynamic shared memory starts a little above address 0; [kWindowLo, kWindowHi) of the dynamic allocation is
+// kept free for the tables for any start below kMaxBase.
+constexpr uint32_t kMaxBase = 4096u;
+constexpr int kWindowLo = (int)(kLutAbs - kMaxBase);          // 61440
+constexpr int kWindowHi = (int)kLutAbs + kLutBytes + 256;     // 72704
+// a byte of 255 at the highest lane reads up to here (absolute): the allocation always reaches it
+constexpr int kMinSmem = (int)kLutAbs + 255 * 256 + 128 + 15 * 8 + 8 + 128;
+constexpr int kSmemBudget = 224 * 1024;
+
+enum { LUT_STATUS_OK = 0, LUT_STATUS_TIMEOUT_PRODUCER = 5, LUT_STATUS_TIMEOUT_CONSUMER = 6, LUT_STATUS_TIMEOUT_EXCHANGE = 7,
+       LUT_STATUS_LAYOUT = 8 };
+__device__ int g_lut_status = 0;
+
+struct LutSeg {
+    const float *row_scale;  // M or null
+    const float *bias;       // M or null
+    void *C;                 // (ntok, M) row-major, ldc elements
+    int64_t M;
+    int tile_begin;          // first row tile (blockIdx.x) of this segment
+};
+
+struct GemvLutParams {
+    LutSeg seg[kMaxSeg];
+    int n_seg;
+    const void *X;           // (ntok, K) row-major, ldx elements
+    int64_t K, kl, ldx, ldc;
+    int ntok;
+    float alpha, beta;
+    int row_warps;           // RW: 32-row groups side by side in a CTA
+    int k_warps;             // KW: slices of the CTA's contraction range
+    int limbs_per_slice;     // limbs per CTA of a cluster, multiple of 4
+    int stages, stage_bytes;
+    int ring0_stages;        // ring slots [0, ring0_stages) lie at offset 0, the others at ring1_offset
+    int ring1_offset, xs_offset, part_offset, sb_offset, bar_offset;
+    int bulk_x;              // 1: bf16 activations, 16-byte aligned rows: fetched by bulk copies
+    int independent;         // 1: reads nothing the previous kernel of the stream wrote
+    int n_peers;             // other GPUs whose result receives every output element too (one segment only)
+    void *peer_C[T81B200_MAX_PEERS];
+    uint32_t *sync_local;
+    uint32_t *sync_peer[T81B200_MAX_PEERS];
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// Table entry of byte value b at an even (which = 0) or odd (which = 1) position of a byte pair.
+//   even: {(t0, t1), (t2, 0)}     odd: {(0, t0), (t1, t2)}      as bf16 pairs, low half first
+__device__ __forceinline__ uint2 lut_entry(int b, int which) {
+    int d0, d1, d2;
+    tryte_digits((uint32_t)b, d0, d1, d2);
+    auto bits = [](int d) -> uint32_t { return d == 0 ? 0xBF80u : (d == 2 ? 0x3F80u : 0u); };  // digit d = trit + 1
+    const uint32_t t0 = bits(d0), t1 = bits(d1), t2 = bits(d2);
+    return which == 0 ? make_uint2(t0 | (t1 << 16), t2) : make_uint2(t0 << 16, t1 | (t2 << 16));
+}
+
+// One 32-bit word of a limb (4 trytes = 12 trits) -> 6 registers of adjacent trit pairs.
+// lane_key = kLutAbs | (lane % 16) * 8.
+__device__ __forceinline__ void lut_decode_word(uint32_t w, uint32_t lane_key, uint32_t (&o)[6]) {
+    uint32_t a0, a1, a2, a3;
+    asm("prmt.b32 %0, %1, %2, 0x7604;" : "=r"(a0) : "r"(w), "r"(lane_key));
+    asm("prmt.b32 %0, %1, %2, 0x7614;" : "=r"(a1) : "r"(w), "r"(lane_key));
+    asm("prmt.b32 %0, %1, %2, 0x7624;" : "=r"(a2) : "r"(w), "r"(lane_key));
+    asm("prmt.b32 %0, %1, %2, 0x7634;" : "=r"(a3) : "r"(w), "r"(lane_key));
+    uint32_t e0x, e0y, o0x, o0y, e1x, e1y, o1x, o1y;
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e0x), "=r"(e0y) : "r"(a0));
+    asm("ld.shared.v2.u32 {%0, %1}, [%2+128];" : "=r"(o0x), "=r"(o0y) : "r"(a1));
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e1x), "=r"(e1y) : "r"(a2));
+    asm("ld.shared.v2.u32 {%0, %1}, [%2+128];" : "=r"(o1x), "=r"(o1y) : "r"(a3));
+    o[0] = e0x; o[1] = e0y | o0x; o[2] = o0y;
+    o[3] = e1x; o[4] = e1y | o1x; o[5] = o1y;
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <typename XT> struct LutPlanes { static constexpr int value = 2; };
+template <> struct LutPlanes<__nv_bfloat16> { static constexpr int value = 1; };
+
+// Activations of limbs [l_begin, l_end) of the CTA's range (limb 0 = limb L0 of the row) for every token, element
+// by element, in natural order, zero beyond K.  Plane 0 holds bf16(x); plane 1 (PLANES == 2) holds bf16(x - plane 0),
+// so that plane 0 + plane 1 carries 16 mantissa bits of an fp32 / fp16 input.
+template <typename XT, int PLANES>
+__device__ __forceinline__ void stage_elements(const GemvLutParams &p, int L0, int l_begin, int l_end, uint32_t *xs,
+                                               int tok_stride, int plane_stride, int tid, int nthreads) {
+    const XT *X = static_cast<const XT *>(p.X);
+    const int per_tok = (l_end - l_begin) * 24;
+    for (int item = tid; item < p.ntok * per_tok; item += nthreads) {
+        const int tok = item / per_tok, r = item - tok * per_tok;
+        const int64_t k = ((int64_t)(L0 + l_begin)) * 48 + 2 * r;
+        const float e0 = k < p.K ? to_float<XT>(X[(int64_t)tok * p.ldx + k]) : 0.0f;
+        const float e1 = k + 1 < p.K ? to_float<XT>(X[(int64_t)tok * p.ldx + k + 1]) : 0.0f;
+        const uint32_t hi = pack_bf16_pair(e0, e1);
+        uint32_t *dst = xs + tok * tok_stride + l_begin * 24 + r;
+        *dst = hi;
+        if constexpr (PLANES == 2) {
+            const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162 *>(&hi);
+            dst[plane_stride] = pack_bf16_pair(e0 - __low2float(hv), e1 - __high2float(hv));
+        }
+    }
+}
+
+template <typename CT>
+__device__ __forceinline__ void store_out(const GemvLutParams &p, const LutSeg &S, const float *sb, int rows_per_cta,
+                                          int r_local, int64_t row, int tok, float acc) {
+    if (row >= S.M || tok >= p.ntok) return;
+    float v = acc * p.alpha * sb[r_local] + sb[rows_per_cta + r_local];
+    CT *c = static_cast<CT *>(S.C) + (int64_t)tok * p.ldc + row;
+    if (p.beta != 0.0f) v += p.beta * to_float<CT>(*c);
+    const CT out = from_float<CT>(v);
+    *c = out;
+    for (int pj = 0; pj < p.n_peers; ++pj) static_cast<CT *>(p.peer_C[pj])[(int64_t)tok * p.ldc + row] = out;
+}
+
+template <typename XT, typename CT, int TOKB>
+__global__ void __launch_bounds__(kThreads, 1)
+gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                     const __grid_constant__ CUtensorMap map2, const GemvLutParams p) {
+    constexpr int PLANES = LutPlanes<XT>::value;
+    constexpr int kTokPad = 8 * TOKB;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t base = smem_u32(smem);
+    if (base >= kMaxBase) {  // the table window was laid out for a lower start of dynamic shared memory
+        if (threadIdx.x == 0) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_LAYOUT);
+        return;
+    }
+    uint8_t *lut = smem + (kLutAbs - base);
+    const int consumer_warps = p.row_warps * p.k_warps;
+    const int consumer_threads = consumer_warps * 32;
+    const int all_threads = consumer_threads + 32;
+    uint32_t *xs = reinterpret_cast<uint32_t *>(smem + p.xs_offset);
+    float *part = reinterpret_cast<float *>(smem + p.part_offset);
+    float *sb = reinterpret_cast<float *>(smem + p.sb_offset);
+    const uint32_t bars = smem_u32(smem + p.bar_offset);
+    auto full_bar = [&](int st) { return bars + 8u * st; };
+    auto empty_bar = [&](int st) { return bars + 8u * (p.stages + st); };
+    const uint32_t x_bar = bars + 8u * (2 * p.stages);
+    auto ring_offset = [&](int st) { return st < p.ring0_stages ? st * p.stage_bytes : p.ring1_offset + (st - p.ring0_stages) * p.stage_bytes; };
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int slices = (int)cluster.num_blocks();
+    const int slice = (int)cluster.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    // which weight matrix this row tile belongs to
+    int sg = 0;
+    while (sg + 1 < p.n_seg && (int)blockIdx.x >= p.seg[sg + 1].tile_begin) ++sg;
+    const LutSeg &S = p.seg[sg];
+    const CUtensorMap *map_w = sg == 0 ? &map0 : (sg == 1 ? &map1 : &map2);
+    const int rows_per_cta = p.row_warps * 32;
+    const int64_t cta_row0 = (int64_t)((int)blockIdx.x - S.tile_begin) * rows_per_cta;
+
+    const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
+    const int L0 = slice * p.limbs_per_slice;
+    int nl = kl4 - L0;
+    nl = nl < 0 ? 0 : (nl > p.limbs_per_slice ? p.limbs_per_slice : nl);
+    const int chunks_cta = nl >> 2;
+    const int tok_stride = p.limbs_per_slice * 24 + 4;  // +16 bytes: conflict-free 128-bit reads across tokens
+    const int plane_stride = p.ntok * tok_stride;
+
+    if (threadIdx.x == 0) {
+        for (int st = 0; st < p.stages; ++st) { mbar_init(full_bar(st), 1); mbar_init(empty_bar(st), p.row_warps); }
+        mbar_init(x_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // decode tables, row scales and biases: none of this is the previous kernel's output
+    for (int e = threadIdx.x; e < 27 * 32; e += all_threads) {
+        const int b = e >> 5, which = (e >> 4) & 1, l = e & 15;
+        *reinterpret_cast<uint2 *>(lut + b * 256 + which * 128 + l * 8) = lut_entry(b, which);
+    }
+    for (int r = threadIdx.x; r < rows_per_cta; r += all_threads) {
+        const int64_t row = cta_row0 + r;
+        sb[r] = row < S.M && S.row_scale ? S.row_scale[row] : 1.0f;
+        sb[rows_per_cta + r] = row < S.M && S.bias ? S.bias[row] : 0.0f;
+    }
+    __syncthreads();
+    // Programmatic dependent launch: a kernel that depends on its predecessor lets its own successor start once
+    // its input is complete (after its wait below); one that does not depend on it lets the successor start at
+    // once and waits for the predecessor at its very end instead, so that "this grid has completed" still implies
+    // "everything before it has".
+    if (p.independent) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    constexpr int NACC = 2;
+    float acc[2][NACC][TOKB][4];
+#pragma unroll
+    for (int gr = 0; gr < 2; ++gr)
+#pragma unroll
+        for (int a = 0; a < NACC; ++a)
+#pragma unroll
+            for (int b = 0; b < TOKB; ++b) acc[gr][a][b][0] = acc[gr][a][b][1] = acc[gr][a][b][2] = acc[gr][a][b][3] = 0.0f;
+    int rw = 0, kw = 0;
+
+    if (warp == consumer_warps) {
+        // ---------------- producer: the weight stream ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int c = 0; c < chunks_cta && ok; ++c) {
+                const int st = c % p.stages;
+                const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
+                ok = mbar_wait(empty_bar(st), phase ^ 1u);
+                if (!ok) break;
+                mbar_arrive_expect_tx(full_bar(st), (uint32_t)p.stage_bytes);
+                tma_load_2d(base + (uint32_t)ring_offset(st), map_w, (L0 + 4 * c) * 16, (int)cta_row0, full_bar(st));
+            }
+            if (!ok) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_TIMEOUT_PRODUCER);
+        }
+        if (!p.independent) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // before this warp's share of the output stores
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
+    } else {
+        // ---------------- consumers ----------------
+        rw = warp % p.row_warps;
+        kw = warp / p.row_warps;
+        if (!p.independent) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
+        if (p.sync_local) {
+            // ... or what the peers stored into this GPU's memory: wait until all of them have published
+            if (threadIdx.x == 0 && !exchange_wait(p.sync_local, p.n_peers))
+                atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_TIMEOUT_EXCHANGE);
+            asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");
+        }
+        // whole limbs below K come by bulk copy (one per token); the limb K ends in and the zero padding up to a
+        // multiple of 4 limbs are written element by element
+        int whole = 0;
+        if (p.bulk_x) {
+            whole = (int)(p.K / 48) - L0;
+            whole = whole < 0 ? 0 : (whole > nl ? nl : whole);
+            if (threadIdx.x == 0) {
+                if (whole > 0) {
+                    const uint32_t bytes = (uint32_t)whole * 96u;
+                    mbar_arrive_expect_tx(x_bar, bytes * (uint32_t)p.ntok);
+                    const __nv_bfloat16 *X = static_cast<const __nv_bfloat16 *>(p.X);
+                    for (int tok = 0; tok < p.ntok; ++tok)
+                        bulk_load(smem_u32(xs + tok * tok_stride), X + (int64_t)tok * p.ldx + (int64_t)L0 * 48, bytes, x_bar);
+                } else {
+                    mbar_arrive(x_bar);
+                }
+            }
+        }
+        stage_elements<XT, PLANES>(p, L0, whole, nl, xs, tok_stride, plane_stride, threadIdx.x, consumer_threads);
+        bool ok = true;
+        if (p.bulk_x) ok = __all_sync(0xffffffffu, mbar_wait(x_bar, 0));
+        asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // consumers only; the producer is streaming
+
+        int tok_off[TOKB];
+#pragma unroll
+        for (int b = 0; b < TOKB; ++b) tok_off[b] = (8 * b + g < p.ntok ? 8 * b + g : 0) * tok_stride + t * 24;
+        const uint32_t lane_off = (uint32_t)((rw * 32 + g) * 64 + t * 16);
+        const uint32_t lane_key = kLutAbs | (uint32_t)((lane & 15) << 3);
+        for (int c = kw; c < chunks_cta && ok; c += p.k_warps) {
+            const int st = c % p.stages;
+            const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(st), phase));
+            if (!ok) break;
+            const uint8_t *tile = smem + ring_offset(st) + lane_off;
+            uint4 limb[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) limb[j] = *reinterpret_cast<const uint4 *>(tile + j * 8 * 64);  // rows g + 8j
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(st));  // the limbs are in registers: the slot can be refilled
+            uint4 xr[TOKB][PLANES][6];
+#pragma unroll
+            for (int b = 0; b < TOKB; ++b)
+#pragma unroll
+                for (int pl = 0; pl < PLANES; ++pl) {
+                    const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96);
+#pragma unroll
+                    for (int q = 0; q < 6; ++q) xr[b][pl][q] = xv[q];
+                }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+#pragma unroll
+                for (int gr = 0; gr < 2; ++gr) {
+                    const uint4 &la = limb[2 * gr], &lb = limb[2 * gr + 1];
+                    const uint32_t wa = w == 0 ? la.x : (w == 1 ? la.y : (w == 2 ? la.z : la.w));
+                    const uint32_t wb = w == 0 ? lb.x : (w == 1 ? lb.y : (w == 2 ? lb.z : lb.w));
+                    uint32_t oa[6], ob[6];
+                    lut_decode_word(wa, lane_key, oa);
+                    lut_decode_word(wb, lane_key, ob);
+#pragma unroll
+                    for (int b = 0; b < TOKB; ++b)
+#pragma unroll
+                        for (int pl = 0; pl < PLANES; ++pl) {
+                            // registers 6w .. 6w+5 of the limb <-> activation registers 6w .. 6w+5
+                            const uint32_t *xw = reinterpret_cast<const uint32_t *>(&xr[b][pl][0]) + 6 * w;
+                            mma_bf16_16816(acc[gr][(3 * w) % NACC][b], oa[0], ob[0], oa[1], ob[1], xw[0], xw[1]);
+                            mma_bf16_16816(acc[gr][(3 * w + 1) % NACC][b], oa[2], ob[2], oa[3], ob[3], xw[2], xw[3]);
+                            mma_bf16_16816(acc[gr][(3 * w + 2) % NACC][b], oa[4], ob[4], oa[5], ob[5], xw[4], xw[5]);
+                        }
+                }
+            }
+        }
+        if (!ok && lane == 0) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_TIMEOUT_CONSUMER);
+
+        // acc[..][b][0]: (row g, token 8b+2t), [1]: (row g, 8b+2t+1), [2]: (row g+8, 8b+2t), [3]: (row g+8, 8b+2t+1)
+        float *pw = part + (size_t)kw * rows_per_cta * kTokPad;
+#pragma unroll
+        for (int gr = 0; gr < 2; ++gr) {
+            const int lr = rw * 32 + gr * 16;
+#pragma unroll
+            for (int b = 0; b < TOKB; ++b) {
+                float r[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) r[i] = acc[gr][0][b][i] + acc[gr][1][b][i];
+                *reinterpret_cast<float2 *>(pw + (lr + g) * kTokPad + 8 * b + 2 * t) = make_float2(r[0], r[1]);
+                *reinterpret_cast<float2 *>(pw + (lr + g + 8) * kTokPad + 8 * b + 2 * t) = make_float2(r[2], r[3]);
+            }
+        }
+    }
+    __syncthreads();
+
+    // Fold the K-slices' partials in a fixed order (deterministic), then, with more than one CTA per cluster, the
+    // ranks' partials through distributed shared memory.
+    const int outs = rows_per_cta * kTokPad;
+    if (slices == 1) {
+        for (int o = threadIdx.x; o < outs; o += all_threads) {
+            // with peers: rows fastest, so that a warp stores runs of consecutive rows of one token over NVLink
+            const int r = p.n_peers > 0 ? o % rows_per_cta : o / kTokPad, tk = p.n_peers > 0 ? o / rows_per_cta : o % kTokPad;
+            const int idx = r * kTokPad + tk;
+            float s = part[idx];
+            for (int w = 1; w < p.k_warps; ++w) s += part[(size_t)w * outs + idx];
+            store_out<CT>(p, S, sb, rows_per_cta, r, cta_row0 + r, tk, s);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < outs; idx += all_threads) {
+            float s = part[idx];
+            for (int w = 1; w < p.k_warps; ++w) s += part[(size_t)w * outs + idx];
+            part[idx] = s;
+        }
+        cluster.sync();
+        // CTA `slice` finishes rows [slice*span, (slice+1)*span) of the tile, summing ranks 0..S-1 in order
+        const int span = (rows_per_cta + slices - 1) / slices;
+        const int lo = slice * span;
+        const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
+        for (int o = threadIdx.x; o < (hi - lo) * kTokPad; o += all_threads) {
+            const int r = lo + (p.n_peers > 0 ? o % (hi - lo) : o / kTokPad), tk = p.n_peers > 0 ? o / (hi - lo) : o % kTokPad;
+            const int idx = r * kTokPad + tk;
+            float s = 0.0f;
+            for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
+            store_out<CT>(p, S, sb, rows_per_cta, r, cta_row0 + r, tk, s);
+        }
+        cluster.sync();  // peers may still be reading this CTA's partials
+    }
+    if (p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.sync_local) {
+        // one system fence per CTA, by the signalling thread after the barrier: the barrier orders the CTA's stores before it
+        __syncthreads();
+        if (threadIdx.x == 0) exchange_signal(p.sync_local, p.sync_peer, p.n_peers, gridDim.x * gridDim.y);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------- host
+
+// Debugging switches, read once per process:
+//   T81B200_GEMV_CFG="row_warps,k_warps,slices"  forces the launch shape (sweeps)
+//   T81B200_NO_PDL=1                              launches without programmatic dependent launch
+struct Switches {
+    int rw = 0, kw = 0, s = 0;
+    bool pdl = true;
+    Switches() {
+        if (const char *env = getenv("T81B200_GEMV_CFG")) sscanf(env, "%d,%d,%d", &rw, &kw, &s);
+        pdl = getenv("T81B200_NO_PDL") == nullptr;
+    }
+};
+const Switches &switches() {
+    static const Switches sw;
+    return sw;
+}
+
+// Everything about a launch that depends only on the weight matrices, the shapes and the dtypes: computed on
+// the first call with that combination and reused afterwards (tensor maps, launch shape, shared-memory layout).
+struct PlanKey {
+    const void *A[kMaxSeg];
+    int64_t M[kMaxSeg];
+    int64_t K;
+    int n_seg, ntok, x_dtype, c_dtype, device;
+    bool operator==(const PlanKey &o) const { return memcmp(this, &o, sizeof *this) == 0; }
+};
+struct PlanKeyHash {
+    size_t operator()(const PlanKey &k) const {
+        const unsigned char *b = reinterpret_cast<const unsigned char *>(&k);
+        uint64_t h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof k; ++i) { h ^= b[i]; h *= 1099511628211ull; }
+        return (size_t)h;
+    }
+};
+struct Plan {
+    bool valid = false;
+    CUtensorMap map[kMaxSeg];
+    int tile_begin[kMaxSeg];
+    int tiles = 0, slices = 1;
+    int row_warps = 0, k_warps = 0, limbs_per_slice = 0, stages = 0, stage_bytes = 0;
+    int ring0_stages = 0, ring1_offset = 0, xs_offset = 0, part_offset = 0, sb_offset = 0, bar_offset = 0;
+    size_t smem = 0;
+};
+std::mutex g_plan_mu;
+std::unordered_map<PlanKey, Plan, PlanKeyHash> g_plans;
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Shared-memory layout for a launch shape; false when it does not fit.
+bool lay_out(Plan &pl, int planes, int ntok, int tokpad, int rwv, int kwv, int lps, int chunks) {
+    const int rows = 32 * rwv;
+    const size_t stage_bytes = (size_t)rows * 64;
+    const size_t xs_bytes = align_up((size_t)planes * ntok * (lps * 24 + 4) * 4, 128);
+    const size_t part_bytes = align_up((size_t)kwv * rows * tokpad * 4, 128);
+    const size_t sb_bytes = align_up((size_t)2 * rows * 4, 128);
+    const size_t bar_bytes = 1024;  // 2 * 48 + 1 barriers
+    size_t off = kWindowHi;
+    pl.xs_offset = (int)off; off += xs_bytes;
+    pl.part_offset = (int)off; off += part_bytes;
+    pl.sb_offset = (int)off; off += sb_bytes;
+    pl.bar_offset = (int)off; off += bar_bytes;
+    if (off > (size_t)kSmemBudget) return false;
+    int stages0 = (int)(kWindowLo / stage_bytes);
+    int stages1 = (int)(((size_t)kSmemBudget - off) / stage_bytes);
+    int stages = stages0 + stages1;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages > chunks) stages = chunks;
+    if (stages < 2 * kwv && stages < chunks) return false;
+    if (stages0 > stages) stages0 = stages;
+    pl.stages = stages;
+    pl.stage_bytes = (int)stage_bytes;
+    pl.ring0_stages = stages0;
+    pl.ring1_offset = (int)off;
+    off += (size_t)(stages - stages0) * stage_bytes;
+    pl.smem = off < (size_t)kMinSmem ? (size_t)kMinSmem : off;
+    return true;
+}
+
+int make_plan(Plan &pl, const PlanKey &key) {
+    const int planes = key.x_dtype == T81B200_BF16 ? 1 : 2;
+    const int tokpad = key.ntok > 8 ? 16 : 8;
+    const int64_t kl = (key.K + 47) / 48;
+    const int kl4 = (int)((kl + 3) & ~(int64_t)3);
+    const int sms = sm_count();
+    const Switches &sw = switches();
+    double best_t = 1e30;
+    Plan best;
+    for (int rwv = 1; rwv <= 8; ++rwv)
+        for (int kwv = 1; rwv * kwv <= kMaxConsumerWarps; ++kwv)
+            for (int s = 1; s <= 4; s *= 2) {
+                if (sw.rw && (rwv != sw.rw || kwv != sw.kw || s != (sw.s ? sw.s : 1))) continue;
+                if (!sw.rw && kwv != 2 && kwv != 4 && kwv != 8) continue;
+                int lps = (kl4 / 4 + s - 1) / s * 4;
+                if (lps < 4) lps = 4;
+                if (s > 1 && (int64_t)(s - 1) * lps >= kl4) continue;  // an empty slice
+                const int chunks = lps / 4;
+                if (kwv > chunks) continue;                            // a warp without work
+                Plan cand;
+                if (!lay_out(cand, planes, key.ntok, tokpad, rwv, kwv, lps, chunks)) continue;
+                const int rows = 32 * rwv;
+                int64_t row_tiles = 0;
+                for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;
+                // Cost model: a warp needs about kChunkCycles per chunk of 32 rows whatever shares its scheduler,
+                // up to four warps per scheduler; a launch has a fixed cost, a cluster adds its fold.
+                // Clusters must fit inside a GPC: fewer CTAs are co-resident than there are SMs.
+                const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : sms - 20);
+                const double waves = ceil((double)row_tiles * s / wave_ctas);
+                const double warps_per_sched = ceil(rwv * kwv / 4.0);
+                const double chunks_per_warp = ceil((double)chunks / kwv);
+                const double chunk_cycles = 1500.0 * (1.0 + 0.35 * (planes * (tokpad / 8) - 1));
+                const double work = chunks_per_warp * chunk_cycles * (warps_per_sched > 3.0 ? warps_per_sched / 3.0 : 1.0) / 1.9e9;
+                const double t = waves * (2.5e-6 + (s > 1 ? 1.0e-6 : 0.0) + work);
+                if (t < best_t) {
+                    best_t = t;
+                    best = cand;
+                    best.row_warps = rwv; best.k_warps = kwv; best.slices = s; best.limbs_per_slice = lps;
+                    best.tiles = (int)row_tiles;
+                }
+            }
+    if (best_t >= 1e30) return T81B200_EALIGN;  // nothing fits: the caller uses the register-prefetch kernel
+    const int rows = 32 * best.row_warps;
+    int tile = 0;
+    for (int i = 0; i < key.n_seg; ++i) {
+        best.tile_begin[i] = tile;
+        tile += (int)((key.M[i] + rows - 1) / rows);
+        if (int rc = make_map_2d(&best.map[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, key.A[i], (uint64_t)kl * 16, (uint64_t)key.M[i],
+                                 (uint64_t)kl * 16, 64, (uint32_t)rows, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return rc;
+    }
+    for (int i = key.n_seg; i < kMaxSeg; ++i) { best.tile_begin[i] = tile; best.map[i] = best.map[0]; }
+    best.valid = true;
+    pl = best;
+    return T81B200_OK;
+}
+
+template <typename XT, typename CT, int TOKB>
+int launch_lut(const Plan &pl, const GemvLutParams &p, cudaStream_t st) {
+    auto kern = gemv_trit_lut_kernel<XT, CT, TOKB>;
+    // the shared-memory limit is a per-device attribute of the function: raised once per device
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    T81_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+        T81_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.tiles, (unsigned)pl.slices, 1);
+    cfg.blockDim = dim3((unsigned)((pl.row_warps * pl.k_warps + 1) * 32), 1, 1);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)pl.slices;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = switches().pdl ? 2 : 1;
+    T81_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, pl.map[0], pl.map[1], pl.map[2], p));
+    return T81B200_OK;
+}
+
+template <typename XT>
+int launch_lut_ct(const Plan &pl, const GemvLutParams &p, int c_dtype, cudaStream_t st) {
+    const bool wide = p.ntok > 8;
+    switch (c_dtype) {
+        case T81B200_F32: return wide ? launch_lut<XT, float, 2>(pl, p, st) : launch_lut<XT, float, 1>(pl, p, st);
+        case T81B200_BF16: return wide ? launch_lut<XT, __nv_bfloat16, 2>(pl, p, st) : launch_lut<XT, __nv_bfloat16, 1>(pl, p, st);
+        case T81B200_F16: return wide ? launch_lut<XT, __half, 2>(pl, p, st) : launch_lut<XT, __half, 1>(pl, p, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
+}
+
+}  // namespace
+
+extern thread_local int g_hint_independent;
+
+// Launch of the table-decode streaming kernel over n_seg weight matrices that share X.  NK layout, ntok in 1..16,
+// every A 16-byte aligned.  Returns T81B200_EALIGN when no launch shape fits (K too long for shared memory).
+int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
+                         void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
+                         int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx) {
+    PlanKey key;
+    memset(&key, 0, sizeof key);
+    for (int i = 0; i < n_seg; ++i) { key.A[i] = A[i]; key.M[i] = M[i]; }
+    key.K = K; key.n_seg = n_seg; key.ntok = ntok; key.x_dtype = x_dtype; key.c_dtype = c_dtype;
+    T81_CUDA_TRY(cudaGetDevice(&key.device));
+    Plan pl;
+    {
+        std::lock_guard<std::mutex> lock(g_plan_mu);
+        auto it = g_plans.find(key);
+        if (it == g_plans.end()) {
+            Plan fresh;
+            if (int rc = make_plan(fresh, key)) return rc;
+            if (g_plans.size() >= 8192) g_plans.clear();  // a bound, not a policy: plans are cheap to rebuild
+            it = g_plans.emplace(key, fresh).first;
+        }
+        pl = it->second;
+    }
+    GemvLutParams p;
+    memset(&p, 0, sizeof p);
+    for (int i = 0; i < kMaxSeg; ++i) {
+        const int j = i < n_seg ? i : 0;
+        p.seg[i].row_scale = row_scale ? row_scale[j] : nullptr;
+        p.seg[i].bias = bias ? bias[j] : nullptr;
+        p.seg[i].C = C[j];
+        p.seg[i].M = M[j];
+        p.seg[i].tile_begin = pl.tile_begin[i];
+    }
+    p.n_seg = n_seg;
+    p.X = X; p.K = K; p.kl = (K + 47) / 48; p.ldx = ldx; p.ldc = ldc; p.ntok = ntok; p.alpha = alpha; p.beta = beta;
+    p.row_warps = pl.row_warps; p.k_warps = pl.k_warps; p.limbs_per_slice = pl.limbs_per_slice;
+    p.stages = pl.stages; p.stage_bytes = pl.stage_bytes; p.ring0_stages = pl.ring0_stages; p.ring1_offset = pl.ring1_offset;
+    p.xs_offset = pl.xs_offset; p.part_offset = pl.part_offset; p.sb_offset = pl.sb_offset; p.bar_offset = pl.bar_offset;
+    p.bulk_x = x_dtype == T81B200_BF16 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && (ldx * 2) % 16 == 0 ? 1 : 0;
+    p.n_peers = ctx ? ctx->n_peers : 0;
+    for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.peer_C[i] = i < p.n_peers ? ctx->peer_C[i] : nullptr;
+    p.sync_local = ctx ? ctx->sync_local : nullptr;
+    for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.sync_peer[i] = p.sync_local && i < ctx->n_peers ? ctx->sync_slots[i] : nullptr;
+    p.independent = (g_hint_independent && !p.sync_local) ? 1 : 0;
+    switch (x_dtype) {
+        case T81B200_BF16: return launch_lut_ct<__nv_bfloat16>(pl, p, c_dtype, st);
+        case T81B200_F32: return launch_lut_ct<float>(pl, p, c_dtype, st);
+        case T81B200_F16: return launch_lut_ct<__half>(pl, p, c_dtype, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
+}
+
+int gemv_trit_lut_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_lut_status, sizeof v) != cudaSuccess) return T81B200_ECUDA;
+    if (reset && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_lut_status, &zero, sizeof zero) != cudaSuccess) return T81B200_ECUDA;
+    }
+    return v;
+}
+
+}  // namespace t81b200

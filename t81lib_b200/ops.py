@@ -214,3 +214,53 @@ def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: 
             _ptr(packed), _ptr(rs), _ptr(B), b_code, code, ldb, _ptr(bs), _ptr(C), c_code, ldc,
             M, N, K, float(alpha), float(beta), _ptr(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return C
+
+
+def gemm_trit_grouped(packed, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
+                      out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0):
+    """TRIT mode for up to ``_capi.MAX_GROUP`` weight matrices that share their activations (q/k/v, gate/up):
+    ``x`` is (tokens, K); returns the list of (tokens, rows_i) results.  With at most 16 tokens the whole
+    group is one kernel launch.  ``outs`` may give the result tensors (same dtype, same leading stride)."""
+    n = len(packed)
+    if not 1 <= n <= _capi.MAX_GROUP:
+        raise ValueError(f"between 1 and {_capi.MAX_GROUP} matrices per group")
+    _require_cuda(x, "x")
+    if x.ndim != 2 or x.shape[1] != K:
+        raise ValueError("rhs dimension does not match ternary weight width")
+    if x.stride(1) != 1 and x.numel() > 0:
+        x = x.contiguous()
+    dev, tokens = x.device, x.shape[0]
+    rows = [int(p.shape[0]) for p in packed]
+    for p in packed:
+        _require_cuda(p, "packed")
+    if outs is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 needs outs")
+        # one allocation, so that every result has the same leading stride
+        whole = torch.empty((tokens, sum(rows)), dtype=out_dtype or x.dtype, device=dev)
+        outs, lo = [], 0
+        for r in rows:
+            outs.append(whole[:, lo:lo + r])
+            lo += r
+    ldcs = {(o.stride(0) if o.shape[0] > 1 else None) for o in outs} - {None}
+    if len(ldcs) > 1 or any(o.stride(1) != 1 or tuple(o.shape) != (tokens, r) or o.dtype != outs[0].dtype
+                            for o, r in zip(outs, rows)):
+        raise ValueError("grouped results must be (tokens, rows_i) tensors of one dtype with one leading stride")
+    ldc = ldcs.pop() if ldcs else max(rows)
+    vp = ctypes.c_void_p
+
+    def f32(t):
+        if t is None:
+            return None
+        if t.dtype != torch.float32 or t.device != dev or not t.is_contiguous():
+            t = t.detach().to(device=dev, dtype=torch.float32).contiguous()
+        return t
+    scales = [f32(t) for t in (row_scales or [None] * n)]
+    bs = [f32(t) for t in (biases or [None] * n)]
+    arr = lambda ts: (vp * n)(*[None if t is None else t.data_ptr() for t in ts])  # noqa: E731
+    ldb = x.stride(0) if tokens > 1 else max(K, 1)
+    with torch.cuda.device(dev):
+        _capi.check(_capi.lib.t81b200_gemm_trit_grouped(
+            n, arr(packed), arr(scales), arr(bs), arr(outs), (ctypes.c_int64 * n)(*rows), _ptr(x), _dtype_code(x, "x"),
+            ldb, _dtype_code(outs[0], "out"), ldc, tokens, K, float(alpha), float(beta), _stream(dev)))
+    return outs

@@ -1,0 +1,82 @@
+"""Child process of tests/test_reference_shim.py: loads the reference's ``t81lib`` pybind module
+built with T81LIB_USE_CUDA=1 against reference_shim/linalg_cuda_shim.cpp (oracle/_ref/cuda) and
+checks it.  ``cpu``: the module loads and reports the backend (no device needed).  ``gpu``: its
+gemm_ternary and elementwise bindings run on the device and agree with the CPU oracle."""
+
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+import oracle  # noqa: E402
+from oracle import ref as oracle_ref  # noqa: E402
+
+
+def finite_limb_operands(rng, M, N, KL, nonzero=10):
+    ta = np.zeros((M, KL * 48), np.int8)
+    tb = np.zeros((KL * 48, N), np.int8)
+    for l in range(KL):
+        ta[:, l * 48:l * 48 + nonzero] = rng.integers(-1, 2, (M, nonzero))
+        tb[l * 48:l * 48 + nonzero] = rng.integers(-1, 2, (nonzero, N))
+    return oracle.pack_trits_rowwise(ta), oracle.pack_trits_columnwise(tb)
+
+
+def check_cpu():
+    mod = oracle_ref.load_cuda()
+    assert mod.HAS_CUDA_BACKEND is True and mod.TRITS_PER_LIMB == 48
+    for name in ("gemm_ternary", "where", "clamp", "lerp", "addcmul", "pack_dense_matrix", "quantize_to_trits",
+                 "unpack_packed_limbs", "dequantize_trits", "spmm_simple"):
+        assert hasattr(mod, name), name
+
+
+def check_gpu():
+    import array
+    import torch
+    mod = oracle_ref.load_cuda()
+    M, N, K = 2, 3, 48
+    zero = np.frombuffer(bytes([13] * 16) * 3, dtype="V16")
+    c_values = array.array("f", [0.0] * (M * N))
+    mod.gemm_ternary(zero[:2].reshape(2, 1), zero.reshape(1, 3), np.frombuffer(c_values, np.float32).reshape(M, N), M, N, K)
+    assert all(abs(v) <= 1e-6 for v in c_values)
+    c_values = array.array("f", [2.0] * (M * N))
+    mod.gemm_ternary(zero[:2].reshape(2, 1), zero.reshape(1, 3), np.frombuffer(c_values, np.float32).reshape(M, N), M, N, K,
+                     alpha=0.0, beta=0.5)
+    assert all(abs(v - 1.0) <= 1e-6 for v in c_values)
+
+    rng = np.random.default_rng(8)
+    M, N, KL = 40, 24, 3
+    A, B = finite_limb_operands(rng, M, N, KL)
+    C0 = rng.normal(size=(M, N)).astype(np.float32)
+    want = oracle.gemm_limb(A, B, C0, M, N, KL * 48, 2.0, 0.25)
+    C = C0.copy()
+    mod.gemm_ternary(A.reshape(-1, 16).view("V16").reshape(M, KL), B.reshape(-1, 16).view("V16").reshape(KL, N), C, M, N,
+                     KL * 48, alpha=2.0, beta=0.25)
+    np.testing.assert_allclose(C, want, rtol=1e-6)
+    dev = torch.device("cuda", 0)
+    Cd = torch.from_numpy(C0).to(dev)
+    mod.gemm_ternary(torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev), Cd, M, N, KL * 48, alpha=2.0, beta=0.25)
+    np.testing.assert_allclose(Cd.cpu().numpy(), want, rtol=1e-6)
+
+    a = rng.normal(size=(37, 19)).astype(np.float32)
+    b = rng.normal(size=(37, 19)).astype(np.float32)
+    c = rng.normal(size=(37, 19)).astype(np.float32)
+    assert np.array_equal(np.asarray(mod.clamp(a, -0.5, 0.5)), oracle.clamp(a, -0.5, 0.5))
+    assert np.array_equal(np.asarray(mod.lerp(a, b, c)), oracle.lerp(a, b, c))
+    assert np.array_equal(np.asarray(mod.addcmul(a, b, c, 0.3)), oracle.addcmul(a, b, c, 0.3))
+    cond = (a > 0).astype(np.float32)
+    assert np.array_equal(np.asarray(mod.where(cond, b, c)), oracle.where(cond, b, c))
+    ta, tb, tc = (torch.from_numpy(v).to(dev) for v in (a, b, c))
+    got = mod.lerp(ta, tb, tc)
+    assert got.is_cuda and np.array_equal(got.cpu().numpy(), oracle.lerp(a, b, c))
+    got = mod.clamp(ta, -0.5, 0.5)
+    assert got.is_cuda and np.array_equal(got.cpu().numpy(), oracle.clamp(a, -0.5, 0.5))
+
+
+if __name__ == "__main__":
+    check_cpu()
+    if sys.argv[1] == "gpu":
+        check_gpu()
+    print("worker ok")

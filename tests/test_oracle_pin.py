@@ -132,3 +132,40 @@ def test_against_compiled_reference_on_random_inputs():
     t81lib.gemm_ternary(A.reshape(-1, 16).view("V16").reshape(M, KL), B.reshape(-1, 16).view("V16").reshape(KL, N),
                         C, M, N, KL * 48, 0.75, -1.5)
     np.testing.assert_allclose(oracle.gemm_limb(A, B, C0, M, N, KL * 48, 0.75, -1.5), C, rtol=2e-7)
+
+
+def test_elementwise_restatements_match_the_compiled_reference():
+    """where / clamp / lerp / addcmul against the reference's CPU code (src/linalg/gemm_dispatch.cpp:147-222)
+    compiled from its sources.  The generic build evaluates one float32 operation per operator and must
+    agree bit for bit; the -mavx512f build lets the compiler fuse multiply-adds, so lerp and addcmul may
+    differ there by one rounding.  One process can hold only one build of the module, hence the child."""
+    import subprocess
+    import sys
+    if not oracle_ref.available():
+        pytest.skip("oracle/_ref not built")
+    code = r'''
+import importlib.util, sys, numpy as np
+sys.path.insert(0, sys.argv[2])
+import oracle
+spec = importlib.util.spec_from_file_location("t81lib", sys.argv[1])
+m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)
+exact = sys.argv[3] == "exact"
+rng = np.random.default_rng(12)
+a, b, c = (rng.normal(size=(61, 23)).astype(np.float32) for _ in range(3))
+cond = (a > 0).astype(np.float32)
+assert np.array_equal(np.asarray(m.where(cond, b, c)), oracle.where(cond, b, c))
+assert np.array_equal(np.asarray(m.clamp(a, -0.5, 0.25)), oracle.clamp(a, -0.5, 0.25))
+for got, want in ((m.lerp(a, b, c), oracle.lerp(a, b, c)), (m.addcmul(a, b, c, 0.3), oracle.addcmul(a, b, c, 0.3))):
+    got = np.asarray(got)
+    if exact:
+        assert np.array_equal(got, want)
+    else:
+        assert np.max(np.abs(got - want)) <= 1e-6 * np.max(np.abs(want))
+print("ok")
+'''
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    variants = [("generic", "exact")] + ([("avx512f", "close")] if oracle_ref.host_has_avx512f() else [])
+    for variant, how in variants:
+        res = subprocess.run([sys.executable, "-c", code, oracle_ref.path(variant), root, how], capture_output=True, text=True)
+        assert res.returncode == 0 and "ok" in res.stdout, f"{variant}: {res.stdout}{res.stderr}"
