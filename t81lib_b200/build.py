@@ -26,6 +26,11 @@ NVCC_FLAGS = [
 ]
 
 
+def _flags() -> list:
+    """The nvcc flags, plus whatever T81B200_NVCC_EXTRA adds (instrumented builds, e.g. -DT81B200_GEMV_TRACE)."""
+    return NVCC_FLAGS + os.environ.get("T81B200_NVCC_EXTRA", "").split()
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -46,7 +51,7 @@ def source_hash() -> str:
         h.update(os.path.basename(d).encode())
         with open(d, "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     return h.hexdigest()
 
 
@@ -78,7 +83,7 @@ def _build_locked(verbose: bool) -> str:
     procs = []
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(_CSRC, src), "-o", obj]
+        cmd = [nvcc, *_flags(), "-c", os.path.join(_CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -774,7 +774,9 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
 
     // Default: the table-decode kernel.  T81B200_GEMV_PATH (read once per process; A/B runs) selects an older
     // kernel instead: "fma" the TMA-fed kernel with arithmetic decode, "ldg" the register-prefetch kernel.
-    static const char path = [] { const char *e = getenv("T81B200_GEMV_PATH"); return e ? e[0] : '\0'; }();
+    static const bool live = getenv("T81B200_GEMV_CFG_LIVE") != nullptr;
+    static char path = [] { const char *e = getenv("T81B200_GEMV_PATH"); return e ? e[0] : '\0'; }();
+    if (live) { const char *e = getenv("T81B200_GEMV_PATH"); path = e ? e[0] : '\0'; }
     if (path == '\0') {
         const float *rs = row_scale, *bs = bias;
         void *cc = C;

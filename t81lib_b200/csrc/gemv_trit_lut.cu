@@ -5,8 +5,9 @@
 //   * the producer thread streams the CTA's weight rows through a shared-memory ring with TMA
 //     (stages of 32*RW rows x 64 bytes = one 4-limb chunk per row); nothing in that stream depends
 //     on the previous kernel of the stream, so it starts before the programmatic-dependent-launch wait;
-//   * the activations arrive with one bulk copy per token (cp.async.bulk, no per-thread round trips)
-//     after that wait, in their natural order;
+//   * the activations arrive by bulk copies (cp.async.bulk, one per token and piece of the contraction range, no
+//     per-thread round trips) after that wait, in their natural order, each piece behind its own barrier so
+//     that the first chunks are multiplied while the rest is still on its way from L2;
 //   * consumer warp (rw, kw) takes chunks kw, kw + KW, ... of rows 32*rw .. 32*rw+31: lane (g, t) reads
 //     limb t of rows g, g+8, g+16, g+24 with 128-bit shared loads and expands every tryte byte with ONE
 //     shared-memory table look-up into exact bf16 {-1,0,+1}: the byte is dropped into bits 8..15 of the
@@ -50,6 +51,7 @@ constexpr int kMaxSeg = T81B200_MAX_GROUP;
 constexpr int kMaxConsumerWarps = 16;
 constexpr int kThreads = (kMaxConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 48;
+constexpr int kXPieces = 4;       // barriers the activations arrive behind
 // The tables sit at this absolute shared-memory address: its bits 8..15 are zero, so a look-up address is
 // this constant with the byte value dropped into byte 1 and the lane offset into byte 0.
 constexpr uint32_t kLutAbs = 0x10000u;
@@ -66,6 +68,26 @@ constexpr int kSmemBudget = 224 * 1024;
 enum { LUT_STATUS_OK = 0, LUT_STATUS_TIMEOUT_PRODUCER = 5, LUT_STATUS_TIMEOUT_CONSUMER = 6, LUT_STATUS_TIMEOUT_EXCHANGE = 7,
        LUT_STATUS_LAYOUT = 8 };
 __device__ int g_lut_status = 0;
+
+#ifdef T81B200_GEMV_TRACE
+// Instrumented build only (never the shipped library): %globaltimer stamps of up to kTraceCtas CTAs of the last
+// kTraceLaunches launches, read back through t81b200_debug_trace.
+constexpr int kTraceLaunches = 64, kTraceCtas = 512, kTraceStamps = 8;
+__device__ unsigned long long g_trace[kTraceLaunches * kTraceCtas * kTraceStamps];
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE_STAMP(i)                                                                                         \
+    do {                                                                                                       \
+        const int cta__ = blockIdx.y * gridDim.x + blockIdx.x;                                                 \
+        if (threadIdx.x == 0 && cta__ < kTraceCtas)                                                            \
+            g_trace[((size_t)(p.trace_slot % kTraceLaunches) * kTraceCtas + cta__) * kTraceStamps + (i)] = globaltimer(); \
+    } while (0)
+#else
+#define TRACE_STAMP(i) do {} while (0)
+#endif
 
 struct LutSeg {
     const float *row_scale;  // M or null
@@ -88,12 +110,13 @@ struct GemvLutParams {
     int stages, stage_bytes;
     int ring0_stages;        // ring slots [0, ring0_stages) lie at offset 0, the others at ring1_offset
     int ring1_offset, xs_offset, part_offset, sb_offset, bar_offset;
-    int bulk_x;              // 1: bf16 activations, 16-byte aligned rows: fetched by bulk copies
+    int bulk_x;              // 1: bf16 activations, 16-byte aligned rows, K % 8 == 0: fetched by bulk copies
     int independent;         // 1: reads nothing the previous kernel of the stream wrote
     int n_peers;             // other GPUs whose result receives every output element too (one segment only)
     void *peer_C[T81B200_MAX_PEERS];
     uint32_t *sync_local;
     uint32_t *sync_peer[T81B200_MAX_PEERS];
+    int trace_slot;          // instrumented builds: which trace record this launch writes
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -110,6 +133,14 @@ __device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+template <typename CT> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) { return pack_bf16_pair(lo, hi); }
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<float>(float lo, float) { return __float_as_uint(lo); }  // unused
+
 // Table entry of byte value b at an even (which = 0) or odd (which = 1) position of a byte pair.
 //   even: {(t0, t1), (t2, 0)}     odd: {(0, t0), (t1, t2)}      as bf16 pairs, low half first
 __device__ __forceinline__ uint2 lut_entry(int b, int which) {
@@ -121,7 +152,7 @@ __device__ __forceinline__ uint2 lut_entry(int b, int which) {
 }
 
 // One 32-bit word of a limb (4 trytes = 12 trits) -> 6 registers of adjacent trit pairs.
-// lane_key = kLutAbs | (lane % 16) * 8.
+// lane_key = the CTA's shared-memory window (top byte) | kLutAbs | (lane % 16) * 8.
 __device__ __forceinline__ void lut_decode_word(uint32_t w, uint32_t lane_key, uint32_t (&o)[6]) {
     uint32_t a0, a1, a2, a3;
     asm("prmt.b32 %0, %1, %2, 0x7604;" : "=r"(a0) : "r"(w), "r"(lane_key));
@@ -146,39 +177,27 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 template <typename XT> struct LutPlanes { static constexpr int value = 2; };
 template <> struct LutPlanes<__nv_bfloat16> { static constexpr int value = 1; };
 
-// Activations of limbs [l_begin, l_end) of the CTA's range (limb 0 = limb L0 of the row) for every token, element
-// by element, in natural order, zero beyond K.  Plane 0 holds bf16(x); plane 1 (PLANES == 2) holds bf16(x - plane 0),
-// so that plane 0 + plane 1 carries 16 mantissa bits of an fp32 / fp16 input.
+// Activations of the CTA's limbs [0, nl) (limb 0 = limb L0 of the row) for every token, element by element
+// (fp32 / fp16 values, unaligned rows), in natural order, zero beyond K.  Plane 0 holds bf16(x); plane 1
+// (PLANES == 2) holds bf16(x - plane 0), so that plane 0 + plane 1 carries 16 mantissa bits of an fp32 / fp16 input.
 template <typename XT, int PLANES>
-__device__ __forceinline__ void stage_elements(const GemvLutParams &p, int L0, int l_begin, int l_end, uint32_t *xs,
-                                               int tok_stride, int plane_stride, int tid, int nthreads) {
+__device__ __forceinline__ void stage_elements(const GemvLutParams &p, int L0, int nl, uint32_t *xs, int tok_stride,
+                                               int plane_stride, int tid, int nthreads) {
     const XT *X = static_cast<const XT *>(p.X);
-    const int per_tok = (l_end - l_begin) * 24;
+    const int per_tok = nl * 24;
     for (int item = tid; item < p.ntok * per_tok; item += nthreads) {
         const int tok = item / per_tok, r = item - tok * per_tok;
-        const int64_t k = ((int64_t)(L0 + l_begin)) * 48 + 2 * r;
+        const int64_t k = (int64_t)L0 * 48 + 2 * r;
         const float e0 = k < p.K ? to_float<XT>(X[(int64_t)tok * p.ldx + k]) : 0.0f;
         const float e1 = k + 1 < p.K ? to_float<XT>(X[(int64_t)tok * p.ldx + k + 1]) : 0.0f;
         const uint32_t hi = pack_bf16_pair(e0, e1);
-        uint32_t *dst = xs + tok * tok_stride + l_begin * 24 + r;
+        uint32_t *dst = xs + tok * tok_stride + r;
         *dst = hi;
         if constexpr (PLANES == 2) {
             const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162 *>(&hi);
             dst[plane_stride] = pack_bf16_pair(e0 - __low2float(hv), e1 - __high2float(hv));
         }
     }
-}
-
-template <typename CT>
-__device__ __forceinline__ void store_out(const GemvLutParams &p, const LutSeg &S, const float *sb, int rows_per_cta,
-                                          int r_local, int64_t row, int tok, float acc) {
-    if (row >= S.M || tok >= p.ntok) return;
-    float v = acc * p.alpha * sb[r_local] + sb[rows_per_cta + r_local];
-    CT *c = static_cast<CT *>(S.C) + (int64_t)tok * p.ldc + row;
-    if (p.beta != 0.0f) v += p.beta * to_float<CT>(*c);
-    const CT out = from_float<CT>(v);
-    *c = out;
-    for (int pj = 0; pj < p.n_peers; ++pj) static_cast<CT *>(p.peer_C[pj])[(int64_t)tok * p.ldc + row] = out;
 }
 
 template <typename XT, typename CT, int TOKB>
@@ -188,12 +207,17 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     constexpr int PLANES = LutPlanes<XT>::value;
     constexpr int kTokPad = 8 * TOKB;
     extern __shared__ __align__(128) uint8_t smem[];
+    TRACE_STAMP(0);
+    // Shared-memory addresses of a CTA in a cluster carry the CTA's rank in their top byte (measured on sm_100a:
+    // rank r sees its dynamic shared memory at r * 0x1000000 + 0x400); the low 24 bits are the offset in its window.
     const uint32_t base = smem_u32(smem);
-    if (base >= kMaxBase) {  // the table window was laid out for a lower start of dynamic shared memory
-        if (threadIdx.x == 0) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_LAYOUT);
-        return;
-    }
-    uint8_t *lut = smem + (kLutAbs - base);
+    const uint32_t window = base & 0xFF000000u, base_off = base & 0x00FFFFFFu;
+    // The table window was laid out for dynamic shared memory starting below kMaxBase.  Should it start higher,
+    // the CTA still walks through every barrier (its cluster peers read its shared memory) but streams nothing,
+    // and the launch reports LUT_STATUS_LAYOUT.
+    const bool layout_ok = base_off < kMaxBase;
+    if (!layout_ok && threadIdx.x == 0) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_LAYOUT);
+    uint8_t *lut = smem + (layout_ok ? kLutAbs - base_off : (uint32_t)kWindowLo);
     const int consumer_warps = p.row_warps * p.k_warps;
     const int consumer_threads = consumer_warps * 32;
     const int all_threads = consumer_threads + 32;
@@ -218,32 +242,25 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     const LutSeg &S = p.seg[sg];
     const CUtensorMap *map_w = sg == 0 ? &map0 : (sg == 1 ? &map1 : &map2);
     const int rows_per_cta = p.row_warps * 32;
+    const int prow = rows_per_cta + 4;  // row pitch of the partial sums, in floats
     const int64_t cta_row0 = (int64_t)((int)blockIdx.x - S.tile_begin) * rows_per_cta;
 
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
     const int L0 = slice * p.limbs_per_slice;
     int nl = kl4 - L0;
     nl = nl < 0 ? 0 : (nl > p.limbs_per_slice ? p.limbs_per_slice : nl);
-    const int chunks_cta = nl >> 2;
+    const int chunks_cta = layout_ok ? nl >> 2 : 0;
     const int tok_stride = p.limbs_per_slice * 24 + 4;  // +16 bytes: conflict-free 128-bit reads across tokens
     const int plane_stride = p.ntok * tok_stride;
 
-    if (threadIdx.x == 0) {
-        for (int st = 0; st < p.stages; ++st) { mbar_init(full_bar(st), 1); mbar_init(empty_bar(st), p.row_warps); }
-        mbar_init(x_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // decode tables, row scales and biases: none of this is the previous kernel's output
-    for (int e = threadIdx.x; e < 27 * 32; e += all_threads) {
-        const int b = e >> 5, which = (e >> 4) & 1, l = e & 15;
-        *reinterpret_cast<uint2 *>(lut + b * 256 + which * 128 + l * 8) = lut_entry(b, which);
-    }
-    for (int r = threadIdx.x; r < rows_per_cta; r += all_threads) {
-        const int64_t row = cta_row0 + r;
-        sb[r] = row < S.M && S.row_scale ? S.row_scale[row] : 1.0f;
-        sb[rows_per_cta + r] = row < S.M && S.bias ? S.bias[row] : 0.0f;
-    }
+    // x arrives in up to kXPieces pieces of x_group chunks each, every piece behind its own barrier: the first
+    // chunks can be multiplied while the rest of the activations is still on its way from L2
+    const int x_group = (chunks_cta + kXPieces - 1) / kXPieces > 0 ? (chunks_cta + kXPieces - 1) / kXPieces : 1;
+    if (threadIdx.x < p.stages) { mbar_init(full_bar(threadIdx.x), 1); mbar_init(empty_bar(threadIdx.x), p.row_warps); }
+    if (threadIdx.x >= kMaxStages && threadIdx.x < kMaxStages + kXPieces) mbar_init(x_bar + 8u * (threadIdx.x - kMaxStages), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    TRACE_STAMP(1);
     // Programmatic dependent launch: a kernel that depends on its predecessor lets its own successor start once
     // its input is complete (after its wait below); one that does not depend on it lets the successor start at
     // once and waits for the predecessor at its very end instead, so that "this grid has completed" still implies
@@ -264,14 +281,18 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         // ---------------- producer: the weight stream ----------------
         if (lane == 0) {
             bool ok = true;
-            for (int c = 0; c < chunks_cta && ok; ++c) {
+            auto load_weights = [&](int c) {
                 const int st = c % p.stages;
                 const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
-                ok = mbar_wait(empty_bar(st), phase ^ 1u);
-                if (!ok) break;
+                if (!mbar_wait(empty_bar(st), phase ^ 1u)) return false;
                 mbar_arrive_expect_tx(full_bar(st), (uint32_t)p.stage_bytes);
                 tma_load_2d(base + (uint32_t)ring_offset(st), map_w, (L0 + 4 * c) * 16, (int)cta_row0, full_bar(st));
-            }
+                return true;
+            };
+            // the ring's first pass needs nothing but the weights: start it before the wait
+            const int first = chunks_cta < p.stages ? chunks_cta : p.stages;
+            for (int c = 0; c < first && ok; ++c) ok = load_weights(c);
+            for (int c = first; c < chunks_cta && ok; ++c) ok = load_weights(c);
             if (!ok) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_TIMEOUT_PRODUCER);
         }
         if (!p.independent) {
@@ -282,48 +303,84 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         // ---------------- consumers ----------------
         rw = warp % p.row_warps;
         kw = warp / p.row_warps;
+        // decode tables, row scales and biases (none of this is the previous kernel's output), while the producer
+        // already streams weights
+        for (int e = threadIdx.x; e < 27 * 32; e += consumer_threads) {
+            const int b = e >> 5, which = (e >> 4) & 1, l = e & 15;
+            *reinterpret_cast<uint2 *>(lut + b * 256 + which * 128 + l * 8) = lut_entry(b, which);
+        }
+        for (int r = threadIdx.x; r < rows_per_cta; r += consumer_threads) {
+            const int64_t row = cta_row0 + r;
+            sb[r] = row < S.M && S.row_scale ? S.row_scale[row] : 1.0f;
+            sb[rows_per_cta + r] = row < S.M && S.bias ? S.bias[row] : 0.0f;
+        }
+        // Activations by bulk copy (bf16, 16-byte aligned rows, K a multiple of 8): the copies bring exactly the
+        // elements below K; what lies between K and the end of the CTA's padded range is zero and is written now,
+        // before the wait.  Otherwise every element is staged by the threads after the wait.
+        int64_t valid = p.K - (int64_t)L0 * 48;  // elements of this CTA's range that exist
+        valid = valid < 0 ? 0 : (valid > (int64_t)nl * 48 ? (int64_t)nl * 48 : valid);
+        if (p.bulk_x) {
+            const int zero_words = nl * 24 - (int)(valid / 2);
+            for (int item = threadIdx.x; item < p.ntok * zero_words; item += consumer_threads) {
+                const int tok = item / zero_words;
+                xs[tok * tok_stride + (int)(valid / 2) + (item - tok * zero_words)] = 0u;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // tables, scales, zero padding
         if (!p.independent) {
             asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         }
+        TRACE_STAMP(2);
         if (p.sync_local) {
             // ... or what the peers stored into this GPU's memory: wait until all of them have published
             if (threadIdx.x == 0 && !exchange_wait(p.sync_local, p.n_peers))
                 atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_TIMEOUT_EXCHANGE);
             asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");
         }
-        // whole limbs below K come by bulk copy (one per token); the limb K ends in and the zero padding up to a
-        // multiple of 4 limbs are written element by element
-        int whole = 0;
+        bool ok = true;
         if (p.bulk_x) {
-            whole = (int)(p.K / 48) - L0;
-            whole = whole < 0 ? 0 : (whole > nl ? nl : whole);
-            if (threadIdx.x == 0) {
-                if (whole > 0) {
-                    const uint32_t bytes = (uint32_t)whole * 96u;
-                    mbar_arrive_expect_tx(x_bar, bytes * (uint32_t)p.ntok);
-                    const __nv_bfloat16 *X = static_cast<const __nv_bfloat16 *>(p.X);
-                    for (int tok = 0; tok < p.ntok; ++tok)
-                        bulk_load(smem_u32(xs + tok * tok_stride), X + (int64_t)tok * p.ldx + (int64_t)L0 * 48, bytes, x_bar);
-                } else {
-                    mbar_arrive(x_bar);
+            if (warp == 0) {
+                // Issuing a bulk copy occupies the copy unit for tens of nanoseconds whichever lane asks, so the
+                // pieces are issued in order.  Piece j holds the elements of chunks [j * x_group, (j + 1) * x_group)
+                // that exist.
+                const __nv_bfloat16 *X = static_cast<const __nv_bfloat16 *>(p.X);
+                auto piece = [&](int j, int &e0, int &e1) {
+                    const int64_t a = (int64_t)192 * x_group * j, b = (int64_t)192 * x_group * (j + 1);
+                    e0 = (int)(a < valid ? a : valid);
+                    e1 = (int)(b < valid ? b : valid);
+                };
+                if (lane < kXPieces) {
+                    int e0, e1;
+                    piece(lane, e0, e1);
+                    if (e1 > e0) mbar_arrive_expect_tx(x_bar + 8u * lane, (uint32_t)(e1 - e0) * 2u * (uint32_t)p.ntok);
+                    else mbar_arrive(x_bar + 8u * lane);
+                }
+                __syncwarp();
+                for (int i = lane; i < kXPieces * p.ntok; i += 32) {
+                    const int j = i / p.ntok, tok = i - j * p.ntok;
+                    int e0, e1;
+                    piece(j, e0, e1);
+                    if (e1 > e0)
+                        bulk_load(smem_u32(xs + tok * tok_stride + e0 / 2), X + (int64_t)tok * p.ldx + (int64_t)L0 * 48 + e0,
+                                  (uint32_t)(e1 - e0) * 2u, x_bar + 8u * j);
                 }
             }
+        } else {
+            stage_elements<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride, threadIdx.x, consumer_threads);
+            asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");
         }
-        stage_elements<XT, PLANES>(p, L0, whole, nl, xs, tok_stride, plane_stride, threadIdx.x, consumer_threads);
-        bool ok = true;
-        if (p.bulk_x) ok = __all_sync(0xffffffffu, mbar_wait(x_bar, 0));
-        asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // consumers only; the producer is streaming
+        TRACE_STAMP(3);
 
         int tok_off[TOKB];
 #pragma unroll
         for (int b = 0; b < TOKB; ++b) tok_off[b] = (8 * b + g < p.ntok ? 8 * b + g : 0) * tok_stride + t * 24;
         const uint32_t lane_off = (uint32_t)((rw * 32 + g) * 64 + t * 16);
-        const uint32_t lane_key = kLutAbs | (uint32_t)((lane & 15) << 3);
+        const uint32_t lane_key = window | kLutAbs | (uint32_t)((lane & 15) << 3);
         for (int c = kw; c < chunks_cta && ok; c += p.k_warps) {
             const int st = c % p.stages;
             const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(st), phase));
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(st), phase) && (!p.bulk_x || mbar_wait(x_bar + 8u * (c / x_group), 0)));
             if (!ok) break;
             const uint8_t *tile = smem + ring_offset(st) + lane_off;
             uint4 limb[4];
@@ -364,56 +421,101 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
             }
         }
         if (!ok && lane == 0) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_TIMEOUT_CONSUMER);
+        TRACE_STAMP(4);
 
         // acc[..][b][0]: (row g, token 8b+2t), [1]: (row g, 8b+2t+1), [2]: (row g+8, 8b+2t), [3]: (row g+8, 8b+2t+1)
-        float *pw = part + (size_t)kw * rows_per_cta * kTokPad;
+        // partials are kept token-major, part[kw][token][row] with rows padded by 4: the eight rows a finishing
+        // thread reads are contiguous, and the four tokens a quad writes fall on different banks
+        float *pw = part + (size_t)kw * kTokPad * prow;
 #pragma unroll
         for (int gr = 0; gr < 2; ++gr) {
-            const int lr = rw * 32 + gr * 16;
+            const int lr = rw * 32 + gr * 16 + g;
 #pragma unroll
             for (int b = 0; b < TOKB; ++b) {
                 float r[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) r[i] = acc[gr][0][b][i] + acc[gr][1][b][i];
-                *reinterpret_cast<float2 *>(pw + (lr + g) * kTokPad + 8 * b + 2 * t) = make_float2(r[0], r[1]);
-                *reinterpret_cast<float2 *>(pw + (lr + g + 8) * kTokPad + 8 * b + 2 * t) = make_float2(r[2], r[3]);
+                pw[(8 * b + 2 * t) * prow + lr] = r[0];
+                pw[(8 * b + 2 * t + 1) * prow + lr] = r[1];
+                pw[(8 * b + 2 * t) * prow + lr + 8] = r[2];
+                pw[(8 * b + 2 * t + 1) * prow + lr + 8] = r[3];
             }
         }
     }
     __syncthreads();
+    TRACE_STAMP(5);
 
     // Fold the K-slices' partials in a fixed order (deterministic), then, with more than one CTA per cluster, the
-    // ranks' partials through distributed shared memory.
-    const int outs = rows_per_cta * kTokPad;
+    // ranks' partials through distributed shared memory.  A finishing thread owns eight consecutive rows of one
+    // token: two 128-bit reads per partial, one 128-bit (16-bit outputs) or two (fp32) stores.
+    const int plane = kTokPad * prow;        // floats per K-slice
+    const int blocks_per_tok = rows_per_cta / 8;
+    const bool vec_store = p.n_peers == 0 && p.beta == 0.0f && reinterpret_cast<uintptr_t>(S.C) % 16 == 0 &&
+                           (p.ldc * (int64_t)sizeof(CT)) % 16 == 0;
+    auto finish = [&](int tok, int r0, const float (&v)[8]) {  // rows r0 .. r0+7 of the tile, one token
+        if (tok >= p.ntok) return;
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = v[i] * p.alpha * sb[r0 + i] + sb[rows_per_cta + r0 + i];
+        const int64_t row = cta_row0 + r0;
+        CT *c = static_cast<CT *>(S.C) + (int64_t)tok * p.ldc + row;
+        if (vec_store && row + 8 <= S.M) {
+            if constexpr (sizeof(CT) == 4) {
+                reinterpret_cast<float4 *>(c)[0] = make_float4(y[0], y[1], y[2], y[3]);
+                reinterpret_cast<float4 *>(c)[1] = make_float4(y[4], y[5], y[6], y[7]);
+            } else {
+                *reinterpret_cast<uint4 *>(c) = make_uint4(pack_pair<CT>(y[0], y[1]), pack_pair<CT>(y[2], y[3]),
+                                                           pack_pair<CT>(y[4], y[5]), pack_pair<CT>(y[6], y[7]));
+            }
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (row + i >= S.M) continue;
+            float out = y[i];
+            if (p.beta != 0.0f) out += p.beta * to_float<CT>(c[i]);
+            const CT o = from_float<CT>(out);
+            c[i] = o;
+            for (int pj = 0; pj < p.n_peers; ++pj) static_cast<CT *>(p.peer_C[pj])[(int64_t)tok * p.ldc + row + i] = o;
+        }
+    };
     if (slices == 1) {
-        for (int o = threadIdx.x; o < outs; o += all_threads) {
-            // with peers: rows fastest, so that a warp stores runs of consecutive rows of one token over NVLink
-            const int r = p.n_peers > 0 ? o % rows_per_cta : o / kTokPad, tk = p.n_peers > 0 ? o / rows_per_cta : o % kTokPad;
-            const int idx = r * kTokPad + tk;
-            float s = part[idx];
-            for (int w = 1; w < p.k_warps; ++w) s += part[(size_t)w * outs + idx];
-            store_out<CT>(p, S, sb, rows_per_cta, r, cta_row0 + r, tk, s);
+        for (int item = threadIdx.x; item < kTokPad * blocks_per_tok; item += all_threads) {
+            const int tok = item / blocks_per_tok, r0 = (item - tok * blocks_per_tok) * 8;
+            float v[8];
+            const float4 *src = reinterpret_cast<const float4 *>(part + tok * prow + r0);
+            float4 lo = src[0], hi = src[1];
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            for (int w = 1; w < p.k_warps; ++w) {
+                src = reinterpret_cast<const float4 *>(part + (size_t)w * plane + tok * prow + r0);
+                lo = src[0]; hi = src[1];
+                v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+            }
+            finish(tok, r0, v);
         }
     } else {
-        for (int idx = threadIdx.x; idx < outs; idx += all_threads) {
+        for (int idx = threadIdx.x; idx < plane; idx += all_threads) {
             float s = part[idx];
-            for (int w = 1; w < p.k_warps; ++w) s += part[(size_t)w * outs + idx];
+            for (int w = 1; w < p.k_warps; ++w) s += part[(size_t)w * plane + idx];
             part[idx] = s;
         }
         cluster.sync();
         // CTA `slice` finishes rows [slice*span, (slice+1)*span) of the tile, summing ranks 0..S-1 in order
-        const int span = (rows_per_cta + slices - 1) / slices;
-        const int lo = slice * span;
-        const int hi = lo + span < rows_per_cta ? lo + span : rows_per_cta;
-        for (int o = threadIdx.x; o < (hi - lo) * kTokPad; o += all_threads) {
-            const int r = lo + (p.n_peers > 0 ? o % (hi - lo) : o / kTokPad), tk = p.n_peers > 0 ? o / (hi - lo) : o % kTokPad;
-            const int idx = r * kTokPad + tk;
-            float s = 0.0f;
-            for (int rk = 0; rk < slices; ++rk) s += cluster.map_shared_rank(part, rk)[idx];
-            store_out<CT>(p, S, sb, rows_per_cta, r, cta_row0 + r, tk, s);
+        const int span = rows_per_cta / slices;  // a multiple of 8: 32*RW rows, 2 or 4 slices
+        const int span_blocks = span / 8;
+        for (int item = threadIdx.x; item < kTokPad * span_blocks; item += all_threads) {
+            const int tok = item / span_blocks, r0 = slice * span + (item - tok * span_blocks) * 8;
+            float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            for (int rk = 0; rk < slices; ++rk) {
+                const float4 *src = reinterpret_cast<const float4 *>(cluster.map_shared_rank(part, rk) + tok * prow + r0);
+                const float4 lo = src[0], hi = src[1];
+                v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+            }
+            finish(tok, r0, v);
         }
         cluster.sync();  // peers may still be reading this CTA's partials
     }
+    TRACE_STAMP(6);
     if (p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.sync_local) {
         // one system fence per CTA, by the signalling thread after the barrier: the barrier orders the CTA's stores before it
@@ -427,16 +529,24 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
 // Debugging switches, read once per process:
 //   T81B200_GEMV_CFG="row_warps,k_warps,slices"  forces the launch shape (sweeps)
 //   T81B200_NO_PDL=1                              launches without programmatic dependent launch
+//   T81B200_GEMV_CFG_LIVE=1                       re-reads T81B200_GEMV_CFG on every call and plans afresh (sweeps
+//                                                 that try many shapes in one process)
 struct Switches {
     int rw = 0, kw = 0, s = 0;
-    bool pdl = true;
-    Switches() {
+    bool pdl = true, live = false;
+    void read_cfg() {
+        rw = kw = s = 0;
         if (const char *env = getenv("T81B200_GEMV_CFG")) sscanf(env, "%d,%d,%d", &rw, &kw, &s);
+    }
+    Switches() {
+        read_cfg();
         pdl = getenv("T81B200_NO_PDL") == nullptr;
+        live = getenv("T81B200_GEMV_CFG_LIVE") != nullptr;
     }
 };
-const Switches &switches() {
-    static const Switches sw;
+Switches &switches() {
+    static Switches sw;
+    if (sw.live) sw.read_cfg();
     return sw;
 }
 
@@ -476,7 +586,7 @@ bool lay_out(Plan &pl, int planes, int ntok, int tokpad, int rwv, int kwv, int l
     const int rows = 32 * rwv;
     const size_t stage_bytes = (size_t)rows * 64;
     const size_t xs_bytes = align_up((size_t)planes * ntok * (lps * 24 + 4) * 4, 128);
-    const size_t part_bytes = align_up((size_t)kwv * rows * tokpad * 4, 128);
+    const size_t part_bytes = align_up((size_t)kwv * tokpad * (rows + 4) * 4, 128);
     const size_t sb_bytes = align_up((size_t)2 * rows * 4, 128);
     const size_t bar_bytes = 1024;  // 2 * 48 + 1 barriers
     size_t off = kWindowHi;
@@ -507,7 +617,7 @@ int make_plan(Plan &pl, const PlanKey &key) {
     const int64_t kl = (key.K + 47) / 48;
     const int kl4 = (int)((kl + 3) & ~(int64_t)3);
     const int sms = sm_count();
-    const Switches &sw = switches();
+    const Switches sw = switches();
     double best_t = 1e30;
     Plan best;
     for (int rwv = 1; rwv <= 8; ++rwv)
@@ -616,6 +726,7 @@ int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const 
     {
         std::lock_guard<std::mutex> lock(g_plan_mu);
         auto it = g_plans.find(key);
+        if (it != g_plans.end() && switches().live) { g_plans.erase(it); it = g_plans.end(); }
         if (it == g_plans.end()) {
             Plan fresh;
             if (int rc = make_plan(fresh, key)) return rc;
@@ -639,12 +750,16 @@ int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const 
     p.row_warps = pl.row_warps; p.k_warps = pl.k_warps; p.limbs_per_slice = pl.limbs_per_slice;
     p.stages = pl.stages; p.stage_bytes = pl.stage_bytes; p.ring0_stages = pl.ring0_stages; p.ring1_offset = pl.ring1_offset;
     p.xs_offset = pl.xs_offset; p.part_offset = pl.part_offset; p.sb_offset = pl.sb_offset; p.bar_offset = pl.bar_offset;
-    p.bulk_x = x_dtype == T81B200_BF16 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && (ldx * 2) % 16 == 0 ? 1 : 0;
+    p.bulk_x = x_dtype == T81B200_BF16 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && (ldx * 2) % 16 == 0 && K % 8 == 0 ? 1 : 0;
     p.n_peers = ctx ? ctx->n_peers : 0;
     for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.peer_C[i] = i < p.n_peers ? ctx->peer_C[i] : nullptr;
     p.sync_local = ctx ? ctx->sync_local : nullptr;
     for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.sync_peer[i] = p.sync_local && i < ctx->n_peers ? ctx->sync_slots[i] : nullptr;
     p.independent = (g_hint_independent && !p.sync_local) ? 1 : 0;
+#ifdef T81B200_GEMV_TRACE
+    static std::atomic<int> trace_counter{0};
+    p.trace_slot = trace_counter.fetch_add(1);
+#endif
     switch (x_dtype) {
         case T81B200_BF16: return launch_lut_ct<__nv_bfloat16>(pl, p, c_dtype, st);
         case T81B200_F32: return launch_lut_ct<float>(pl, p, c_dtype, st);
@@ -652,6 +767,14 @@ int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const 
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
 }
+
+#ifdef T81B200_GEMV_TRACE
+extern "C" __attribute__((visibility("default"))) int t81b200_debug_trace(unsigned long long *out, int words) {
+    const size_t total = (size_t)kTraceLaunches * kTraceCtas * kTraceStamps;
+    if ((size_t)words > total) words = (int)total;
+    return cudaMemcpyFromSymbol(out, g_trace, (size_t)words * 8) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int gemv_trit_lut_status(int reset) {
     int v = 0;

@@ -1,6 +1,9 @@
 """Column-sharded ternary Linear: output features are split across the ranks of a
 process group (one process per GPU); each rank quantises, packs and multiplies
-only its slice of rows, and one all-gather over NVLink assembles the result.
+only its slice of rows.  The result is assembled either by one all-gather
+(``exchange="collective"``, any backend) or by the matmul kernel itself storing its
+column block into every peer's result over NVLink, ordered by flag words
+(``exchange="p2p"``, CUDA, one node).
 
 Row-wise packing and per-row scales make a shard self-contained: the packed
 bytes of rank r's slice equal rows [r*out/R, (r+1)*out/R) of the unsharded
@@ -119,12 +122,17 @@ class PeerColumns:
     no token-major re-copy of a rank-major gather buffer.
 
     Construction is collective (handles are exchanged through the process group).  ``copies``
-    buffers are handed out round-robin so that a push may still be in flight while the next
-    matmul fills another buffer.  CUDA only; ranks must be processes of one node that see the
-    same GPUs in the same order."""
+    buffers are handed out round-robin.  How long a result lives: the flag protocol lets a peer
+    start call j + 1 as soon as this rank has COMPLETED call j, and that call j + 1 stores into
+    buffer (j + 1) % copies of this rank.  Work this rank queues on its stream before it issues call
+    j + c - 1 of this shape has finished by then, so with ``copies = c`` result j may be read by
+    anything queued before the (c - 1)-th following call of the same shape; later readers must clone
+    it first.  The default of three buffers gives every result a lifetime of two following calls
+    (``a = L1(x); b = L2(a); out = a + b`` is safe).  CUDA only; ranks must be processes of one node
+    that see the same GPUs in the same order."""
 
     def __init__(self, tokens: int, out_features: int, dtype: torch.dtype, device: torch.device, group=None,
-                 copies: int = 2):
+                 copies: int = 3):
         from torch.multiprocessing.reductions import reduce_tensor
         if device.type != "cuda":
             raise ValueError("PeerColumns needs CUDA tensors (there is no CPU path)")
@@ -187,8 +195,9 @@ class ShardedLinear(nn.Module):
         # rank (2.67 bits per weight); the shard is then a view of it, not a second copy.
         self.shard_min_tokens = shard_min_tokens
         # "collective": one all_gather_into_tensor per call (any backend).  "p2p": stores into the peers'
-        # results over NVLink (CUDA, one node); the result is then one of two shared buffers per shape and
-        # is reused two calls of that shape later.
+        # results over NVLink (CUDA, one node); the result is then one of three shared buffers per shape:
+        # it may be read by work queued before the second following p2p call of that shape is issued
+        # (see PeerColumns); clone it to keep it longer.
         if exchange not in ("collective", "p2p"):
             raise ValueError(f"unknown exchange {exchange!r}")
         self.exchange = exchange
@@ -248,8 +257,9 @@ class ShardedLinear(nn.Module):
         return gather_columns(local, self.group)
 
     # Result buffers are shared by every p2p layer of a process with the same (group, device, tokens, width,
-    # dtype): a stack of layers needs two buffers per width, not two per layer.  A result therefore stays
-    # valid until two more calls of that shape have been issued.
+    # dtype): a stack of layers needs three buffers per width, not three per layer.  A result stays valid
+    # for readers queued before the second following call of that shape is issued (PeerColumns explains why
+    # that takes three buffers under the flag protocol).
     _shared_exchanges: dict = {}
 
     def exchange_for(self, tokens: int, dtype: torch.dtype, device: torch.device) -> PeerColumns:

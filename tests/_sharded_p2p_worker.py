@@ -48,6 +48,23 @@ def main() -> int:
     layer.exchange_for(8, torch.bfloat16, dev).flags.wait()
     torch.cuda.synchronize()
     ok = ok and torch.equal(outs[-1], want) and torch.equal(outs[-2], want)
+    # A result is read AFTER the next same-shape call has been issued, while the peer runs ahead: rank 0 stalls
+    # its stream before the read, the other ranks go on issuing calls that store into rank 0's buffers.  With
+    # three buffers per shape the peers' stores of call j + 2 cannot land in the buffer that holds result j.
+    x1 = torch.randn(8, 520, generator=gen, device=dev).to(torch.bfloat16)
+    x2 = torch.randn(8, 520, generator=gen, device=dev).to(torch.bfloat16)
+    want_sum = full.matmul_input(x1, bias=b).float() + full.matmul_input(x2, bias=b).float()
+    for _ in range(4):
+        ra = layer(x1)
+        rb = layer(x2)
+        if rank == 0:
+            torch.cuda._sleep(20_000_000)  # ~10 ms: the peers get far ahead of this stream
+        layer.exchange_for(8, torch.bfloat16, dev).flags.wait()  # the peers' blocks of call j + 1 have landed
+        total = ra.float() + rb.float()    # reads result j after call j + 1 was issued
+        layer(x)                           # call j + 2 (stores into a third buffer on every rank)
+        layer.exchange_for(8, torch.bfloat16, dev).flags.wait()
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(total, want_sum)
     ok = ok and _capi.kernel_status(reset=True) == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
