@@ -635,16 +635,20 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 const int rows = 32 * rwv;
                 int64_t row_tiles = 0;
                 for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;
-                // Cost model: a warp needs about kChunkCycles per chunk of 32 rows whatever shares its scheduler,
-                // up to four warps per scheduler; a launch has a fixed cost, a cluster adds its fold.
+                // Cost model, fitted to a sweep of every launch shape over the Llama- and Phi-shaped layers (mean
+                // regret 2.5 %): a warp needs about a microsecond per chunk of 32 rows whatever shares its
+                // scheduler, up to four warps per scheduler; every CTA pulls its own copy of its slice of the
+                // activations out of L2, which delivers about 3 TB/s when all CTAs ask for the same lines at once;
+                // the longer of the two bounds the CTA; a launch costs 2 us, a cluster's fold 1 us more.
                 // Clusters must fit inside a GPC: fewer CTAs are co-resident than there are SMs.
                 const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : sms - 20);
                 const double waves = ceil((double)row_tiles * s / wave_ctas);
                 const double warps_per_sched = ceil(rwv * kwv / 4.0);
                 const double chunks_per_warp = ceil((double)chunks / kwv);
-                const double chunk_cycles = 1500.0 * (1.0 + 0.35 * (planes * (tokpad / 8) - 1));
-                const double work = chunks_per_warp * chunk_cycles * (warps_per_sched > 3.0 ? warps_per_sched / 3.0 : 1.0) / 1.9e9;
-                const double t = waves * (2.5e-6 + (s > 1 ? 1.0e-6 : 0.0) + work);
+                const double work = chunks_per_warp * 1.0e-6 * (1.0 + 0.6 * (planes * (tokpad / 8) - 1)) *
+                                    (warps_per_sched > 4.0 ? warps_per_sched / 4.0 : 1.0);
+                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / 3.0e12;
+                const double t = waves * (2.0e-6 + (s > 1 ? 1.0e-6 : 0.0) + (work > x_fetch ? work : x_fetch));
                 if (t < best_t) {
                     best_t = t;
                     best = cand;
