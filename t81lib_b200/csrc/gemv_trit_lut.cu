@@ -25,9 +25,9 @@
 // row tiles are numbered through the segments.
 //
 // Bytes above 26 are not valid trytes (the packer never writes them; limb::from_bytes of the reference
-// rejects them, include/t81/core/limb.hpp:160-169).  Here they index past the 27 table entries into other
-// shared memory of the CTA: the affected outputs are unspecified, and the launch keeps its allocation
-// large enough that no such read can leave it.
+// rejects them, include/t81/core/limb.hpp:160-169).  Every weight word is masked to five bits per byte before
+// it is used as a table index and the table has 32 entries per position, the last five all zero: bytes 27..31
+// decode as the zero tryte and larger ones as some valid tryte; no look-up can leave the table.
 #include "common.cuh"
 #include "tma.cuh"
 #include "exchange.cuh"
@@ -55,14 +55,12 @@ constexpr int kXPieces = 4;       // barriers the activations arrive behind
 // The tables sit at this absolute shared-memory address: its bits 8..15 are zero, so a look-up address is
 // this constant with the byte value dropped into byte 1 and the lane offset into byte 0.
 constexpr uint32_t kLutAbs = 0x10000u;
-constexpr int kLutBytes = 27 * 256;
+constexpr int kLutBytes = 32 * 256;
 // Dynamic shared memory starts a little above address 0; [kWindowLo, kWindowHi) of the dynamic allocation is
 // kept free for the tables for any start below kMaxBase.
 constexpr uint32_t kMaxBase = 4096u;
 constexpr int kWindowLo = (int)(kLutAbs - kMaxBase);          // 61440
-constexpr int kWindowHi = (int)kLutAbs + kLutBytes + 256;     // 72704
-// a byte of 255 at the highest lane reads up to here (absolute): the allocation always reaches it
-constexpr int kMinSmem = (int)kLutAbs + 255 * 256 + 128 + 15 * 8 + 8 + 128;
+constexpr int kWindowHi = (int)kLutAbs + kLutBytes + 256;     // 73984
 constexpr int kSmemBudget = 224 * 1024;
 
 enum { LUT_STATUS_OK = 0, LUT_STATUS_TIMEOUT_PRODUCER = 5, LUT_STATUS_TIMEOUT_CONSUMER = 6, LUT_STATUS_TIMEOUT_EXCHANGE = 7,
@@ -141,15 +139,28 @@ template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, floa
 }
 template <> __device__ __forceinline__ uint32_t pack_pair<float>(float lo, float) { return __float_as_uint(lo); }  // unused
 
-// Table entry of byte value b at an even (which = 0) or odd (which = 1) position of a byte pair.
-//   even: {(t0, t1), (t2, 0)}     odd: {(0, t0), (t1, t2)}      as bf16 pairs, low half first
-__device__ __forceinline__ uint2 lut_entry(int b, int which) {
-    int d0, d1, d2;
-    tryte_digits((uint32_t)b, d0, d1, d2);
-    auto bits = [](int d) -> uint32_t { return d == 0 ? 0xBF80u : (d == 2 ? 0x3F80u : 0u); };  // digit d = trit + 1
-    const uint32_t t0 = bits(d0), t1 = bits(d1), t2 = bits(d2);
-    return which == 0 ? make_uint2(t0 | (t1 << 16), t2) : make_uint2(t0 << 16, t1 | (t2 << 16));
+// The decode tables as they lie in shared memory: [byte value 0..31][even / odd position][16 lane copies] of
+// 64-bit entries, 8 KB, built at compile time and copied into every CTA by one bulk copy.
+//   even position: {(t0, t1), (t2, 0)}     odd position: {(0, t0), (t1, t2)}      bf16 pairs, low half first
+// Values 27..31 are not trytes: their entries are zero.
+struct LutImage {
+    uint32_t w[32 * 2 * 16 * 2];
+};
+constexpr uint32_t trit_bits(int d) { return d == 0 ? 0xBF80u : (d == 2 ? 0x3F80u : 0u); }  // digit d = trit + 1
+constexpr LutImage make_lut_image() {
+    LutImage im{};
+    for (int b = 0; b < 32; ++b) {
+        const uint32_t t0 = b < 27 ? trit_bits(b % 3) : 0u, t1 = b < 27 ? trit_bits((b / 3) % 3) : 0u, t2 = b < 27 ? trit_bits(b / 9) : 0u;
+        for (int l = 0; l < 16; ++l) {
+            im.w[((b * 2 + 0) * 16 + l) * 2 + 0] = t0 | (t1 << 16);
+            im.w[((b * 2 + 0) * 16 + l) * 2 + 1] = t2;
+            im.w[((b * 2 + 1) * 16 + l) * 2 + 0] = t0 << 16;
+            im.w[((b * 2 + 1) * 16 + l) * 2 + 1] = t1 | (t2 << 16);
+        }
+    }
+    return im;
 }
+__device__ __align__(128) const LutImage g_lut_image = make_lut_image();
 
 // One 32-bit word of a limb (4 trytes = 12 trits) -> 6 registers of adjacent trit pairs.
 // lane_key = the CTA's shared-memory window (top byte) | kLutAbs | (lane % 16) * 8.
@@ -228,6 +239,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     auto full_bar = [&](int st) { return bars + 8u * st; };
     auto empty_bar = [&](int st) { return bars + 8u * (p.stages + st); };
     const uint32_t x_bar = bars + 8u * (2 * p.stages);
+    const uint32_t pro_bar = x_bar + 8u * kXPieces;  // decode tables, row scales and biases have landed
     auto ring_offset = [&](int st) { return st < p.ring0_stages ? st * p.stage_bytes : p.ring1_offset + (st - p.ring0_stages) * p.stage_bytes; };
 
     cg::cluster_group cluster = cg::this_cluster();
@@ -245,6 +257,10 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     const int prow = rows_per_cta + 4;  // row pitch of the partial sums, in floats
     const int64_t cta_row0 = (int64_t)((int)blockIdx.x - S.tile_begin) * rows_per_cta;
 
+    const bool whole_tile = cta_row0 + rows_per_cta <= S.M;
+    const bool scale_by_copy = layout_ok && S.row_scale && whole_tile && reinterpret_cast<uintptr_t>(S.row_scale) % 16 == 0;
+    const bool bias_by_copy = layout_ok && S.bias && whole_tile && reinterpret_cast<uintptr_t>(S.bias) % 16 == 0;
+
     const int kl4 = (int)((p.kl + 3) & ~(int64_t)3);
     const int L0 = slice * p.limbs_per_slice;
     int nl = kl4 - L0;
@@ -258,6 +274,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     const int x_group = (chunks_cta + kXPieces - 1) / kXPieces > 0 ? (chunks_cta + kXPieces - 1) / kXPieces : 1;
     if (threadIdx.x < p.stages) { mbar_init(full_bar(threadIdx.x), 1); mbar_init(empty_bar(threadIdx.x), p.row_warps); }
     if (threadIdx.x >= kMaxStages && threadIdx.x < kMaxStages + kXPieces) mbar_init(x_bar + 8u * (threadIdx.x - kMaxStages), 1);
+    if (threadIdx.x == kMaxStages + kXPieces) mbar_init(pro_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
     TRACE_STAMP(1);
@@ -266,6 +283,37 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     // once and waits for the predecessor at its very end instead, so that "this grid has completed" still implies
     // "everything before it has".
     if (p.independent) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // Activations by bulk copy (bf16, 16-byte aligned rows, K a multiple of 8): the copies bring exactly the
+    // elements below K, one copy per token and piece; piece j holds the elements of chunks
+    // [j * x_group, (j + 1) * x_group) that exist.  Issuing a copy costs its warp tens of nanoseconds, so the
+    // consumer warps share them out (lane 0 of each), in piece order: no warp starts its chunks late.
+    int64_t valid = p.K - (int64_t)L0 * 48;  // elements of this CTA's range that exist
+    valid = valid < 0 ? 0 : (valid > (int64_t)nl * 48 ? (int64_t)nl * 48 : valid);
+    auto x_piece = [&](int j, int &e0, int &e1) {
+        const int64_t a = (int64_t)192 * x_group * j, b = (int64_t)192 * x_group * (j + 1);
+        e0 = (int)(a < valid ? a : valid);
+        e1 = (int)(b < valid ? b : valid);
+    };
+    auto expect_x = [&]() {  // one thread, before any copy is issued
+        for (int j = 0; j < kXPieces; ++j) {
+            int e0, e1;
+            x_piece(j, e0, e1);
+            if (e1 > e0) mbar_arrive_expect_tx(x_bar + 8u * j, (uint32_t)(e1 - e0) * 2u * (uint32_t)p.ntok);
+            else mbar_arrive(x_bar + 8u * j);
+        }
+    };
+    auto issue_x = [&](int who, int n_who) {  // copies who, who + n_who, ... in piece order
+        const __nv_bfloat16 *X = static_cast<const __nv_bfloat16 *>(p.X);
+        for (int i = who; i < kXPieces * p.ntok; i += n_who) {
+            const int j = i / p.ntok, tok = i - j * p.ntok;
+            int e0, e1;
+            x_piece(j, e0, e1);
+            if (e1 > e0)
+                bulk_load(smem_u32(xs + tok * tok_stride + e0 / 2), X + (int64_t)tok * p.ldx + (int64_t)L0 * 48 + e0,
+                          (uint32_t)(e1 - e0) * 2u, x_bar + 8u * j);
+        }
+    };
 
     constexpr int NACC = 2;
     float acc[2][NACC][TOKB][4];
@@ -289,6 +337,18 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
                 tma_load_2d(base + (uint32_t)ring_offset(st), map_w, (L0 + 4 * c) * 16, (int)cta_row0, full_bar(st));
                 return true;
             };
+            // decode tables (a compile-time image in global memory), row scales and biases: bulk copies, none of
+            // them the previous kernel's output.  Scales and biases that a copy cannot take (unaligned, or a tile
+            // that reaches past the last row) are fetched by the consumer threads instead.
+            if (layout_ok) {
+                uint32_t bytes = (uint32_t)kLutBytes;
+                if (scale_by_copy) bytes += (uint32_t)rows_per_cta * 4u;
+                if (bias_by_copy) bytes += (uint32_t)rows_per_cta * 4u;
+                mbar_arrive_expect_tx(pro_bar, bytes);
+                bulk_load(smem_u32(lut), &g_lut_image, (uint32_t)kLutBytes, pro_bar);
+                if (scale_by_copy) bulk_load(smem_u32(sb), S.row_scale + cta_row0, (uint32_t)rows_per_cta * 4u, pro_bar);
+                if (bias_by_copy) bulk_load(smem_u32(sb + rows_per_cta), S.bias + cta_row0, (uint32_t)rows_per_cta * 4u, pro_bar);
+            }
             // the ring's first pass needs nothing but the weights: start it before the wait
             const int first = chunks_cta < p.stages ? chunks_cta : p.stages;
             for (int c = 0; c < first && ok; ++c) ok = load_weights(c);
@@ -303,22 +363,14 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         // ---------------- consumers ----------------
         rw = warp % p.row_warps;
         kw = warp / p.row_warps;
-        // decode tables, row scales and biases (none of this is the previous kernel's output), while the producer
-        // already streams weights
-        for (int e = threadIdx.x; e < 27 * 32; e += consumer_threads) {
-            const int b = e >> 5, which = (e >> 4) & 1, l = e & 15;
-            *reinterpret_cast<uint2 *>(lut + b * 256 + which * 128 + l * 8) = lut_entry(b, which);
-        }
-        for (int r = threadIdx.x; r < rows_per_cta; r += consumer_threads) {
-            const int64_t row = cta_row0 + r;
-            sb[r] = row < S.M && S.row_scale ? S.row_scale[row] : 1.0f;
-            sb[rows_per_cta + r] = row < S.M && S.bias ? S.bias[row] : 0.0f;
-        }
-        // Activations by bulk copy (bf16, 16-byte aligned rows, K a multiple of 8): the copies bring exactly the
-        // elements below K; what lies between K and the end of the CTA's padded range is zero and is written now,
-        // before the wait.  Otherwise every element is staged by the threads after the wait.
-        int64_t valid = p.K - (int64_t)L0 * 48;  // elements of this CTA's range that exist
-        valid = valid < 0 ? 0 : (valid > (int64_t)nl * 48 ? (int64_t)nl * 48 : valid);
+        // row scales and biases the producer's bulk copies do not bring (see there); absent ones are 1 and 0
+        if (!scale_by_copy)
+            for (int r = threadIdx.x; r < rows_per_cta; r += consumer_threads)
+                sb[r] = cta_row0 + r < S.M && S.row_scale ? S.row_scale[cta_row0 + r] : 1.0f;
+        if (!bias_by_copy)
+            for (int r = threadIdx.x; r < rows_per_cta; r += consumer_threads)
+                sb[rows_per_cta + r] = cta_row0 + r < S.M && S.bias ? S.bias[cta_row0 + r] : 0.0f;
+        // what lies between K and the end of the CTA's padded range is zero and is written now, before the wait
         if (p.bulk_x) {
             const int zero_words = nl * 24 - (int)(valid / 2);
             for (int item = threadIdx.x; item < p.ntok * zero_words; item += consumer_threads) {
@@ -326,7 +378,8 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
                 xs[tok * tok_stride + (int)(valid / 2) + (item - tok * zero_words)] = 0u;
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // tables, scales, zero padding
+        if (p.bulk_x && threadIdx.x == 0) expect_x();
+        asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");  // thread-written scales, zero padding, expected bytes
         if (!p.independent) {
             asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may be the previous kernel's output
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -340,32 +393,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         }
         bool ok = true;
         if (p.bulk_x) {
-            if (warp == 0) {
-                // Issuing a bulk copy occupies the copy unit for tens of nanoseconds whichever lane asks, so the
-                // pieces are issued in order.  Piece j holds the elements of chunks [j * x_group, (j + 1) * x_group)
-                // that exist.
-                const __nv_bfloat16 *X = static_cast<const __nv_bfloat16 *>(p.X);
-                auto piece = [&](int j, int &e0, int &e1) {
-                    const int64_t a = (int64_t)192 * x_group * j, b = (int64_t)192 * x_group * (j + 1);
-                    e0 = (int)(a < valid ? a : valid);
-                    e1 = (int)(b < valid ? b : valid);
-                };
-                if (lane < kXPieces) {
-                    int e0, e1;
-                    piece(lane, e0, e1);
-                    if (e1 > e0) mbar_arrive_expect_tx(x_bar + 8u * lane, (uint32_t)(e1 - e0) * 2u * (uint32_t)p.ntok);
-                    else mbar_arrive(x_bar + 8u * lane);
-                }
-                __syncwarp();
-                for (int i = lane; i < kXPieces * p.ntok; i += 32) {
-                    const int j = i / p.ntok, tok = i - j * p.ntok;
-                    int e0, e1;
-                    piece(j, e0, e1);
-                    if (e1 > e0)
-                        bulk_load(smem_u32(xs + tok * tok_stride + e0 / 2), X + (int64_t)tok * p.ldx + (int64_t)L0 * 48 + e0,
-                                  (uint32_t)(e1 - e0) * 2u, x_bar + 8u * j);
-                }
-            }
+            if (lane == 0) issue_x(warp, consumer_warps);
         } else {
             stage_elements<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride, threadIdx.x, consumer_threads);
             asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");
@@ -377,6 +405,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         for (int b = 0; b < TOKB; ++b) tok_off[b] = (8 * b + g < p.ntok ? 8 * b + g : 0) * tok_stride + t * 24;
         const uint32_t lane_off = (uint32_t)((rw * 32 + g) * 64 + t * 16);
         const uint32_t lane_key = window | kLutAbs | (uint32_t)((lane & 15) << 3);
+        if (layout_ok) ok = __all_sync(0xffffffffu, mbar_wait(pro_bar, 0));
         for (int c = kw; c < chunks_cta && ok; c += p.k_warps) {
             const int st = c % p.stages;
             const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
@@ -385,7 +414,10 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
             const uint8_t *tile = smem + ring_offset(st) + lane_off;
             uint4 limb[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) limb[j] = *reinterpret_cast<const uint4 *>(tile + j * 8 * 64);  // rows g + 8j
+            for (int j = 0; j < 4; ++j) {  // rows g + 8j; five bits per byte: no table index can leave the table
+                limb[j] = *reinterpret_cast<const uint4 *>(tile + j * 8 * 64);
+                limb[j].x &= 0x1F1F1F1Fu; limb[j].y &= 0x1F1F1F1Fu; limb[j].z &= 0x1F1F1F1Fu; limb[j].w &= 0x1F1F1F1Fu;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(st));  // the limbs are in registers: the slot can be refilled
             uint4 xr[TOKB][PLANES][6];
@@ -446,7 +478,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     TRACE_STAMP(5);
 
     // Fold the K-slices' partials in a fixed order (deterministic), then, with more than one CTA per cluster, the
-    // ranks' partials through distributed shared memory.  A finishing thread owns eight consecutive rows of one
+    // ranks' partials through distributed shared memory (also in a fixed order).  A finishing thread owns eight consecutive rows of one
     // token: two 128-bit reads per partial, one 128-bit (16-bit outputs) or two (fp32) stores.
     const int plane = kTokPad * prow;        // floats per K-slice
     const int blocks_per_tok = rows_per_cta / 8;
@@ -494,26 +526,40 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
             finish(tok, r0, v);
         }
     } else {
-        for (int idx = threadIdx.x; idx < plane; idx += all_threads) {
-            float s = part[idx];
-            for (int w = 1; w < p.k_warps; ++w) s += part[(size_t)w * plane + idx];
-            part[idx] = s;
+        // Push: every CTA sums its K-slices and writes each block of rows into the receive buffer of the CTA that
+        // finishes those rows (slot = the sender's rank), one cluster barrier orders the writes before the reads,
+        // and the finisher adds the slots in rank order.  After the barrier no CTA touches another's memory, so
+        // none has to outlive the others.
+        const int span = rows_per_cta / slices;  // a multiple of 8: 32*RW rows, 2 or 4 slices
+        const int spitch = span + 4;
+        const int slot = kTokPad * spitch;       // floats per sender
+        float *recv = part + (size_t)p.k_warps * plane;
+        for (int item = threadIdx.x; item < kTokPad * blocks_per_tok; item += all_threads) {
+            const int tok = item / blocks_per_tok, r0 = (item - tok * blocks_per_tok) * 8;
+            const float4 *src = reinterpret_cast<const float4 *>(part + tok * prow + r0);
+            float4 lo = src[0], hi = src[1];
+            for (int w = 1; w < p.k_warps; ++w) {
+                src = reinterpret_cast<const float4 *>(part + (size_t)w * plane + tok * prow + r0);
+                const float4 a = src[0], b = src[1];
+                lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w; hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+            }
+            const int dst = r0 / span;
+            float4 *out = reinterpret_cast<float4 *>(cluster.map_shared_rank(recv, dst) + (size_t)slice * slot + tok * spitch + (r0 - dst * span));
+            out[0] = lo;
+            out[1] = hi;
         }
         cluster.sync();
-        // CTA `slice` finishes rows [slice*span, (slice+1)*span) of the tile, summing ranks 0..S-1 in order
-        const int span = rows_per_cta / slices;  // a multiple of 8: 32*RW rows, 2 or 4 slices
         const int span_blocks = span / 8;
         for (int item = threadIdx.x; item < kTokPad * span_blocks; item += all_threads) {
-            const int tok = item / span_blocks, r0 = slice * span + (item - tok * span_blocks) * 8;
+            const int tok = item / span_blocks, r0 = (item - tok * span_blocks) * 8;
             float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             for (int rk = 0; rk < slices; ++rk) {
-                const float4 *src = reinterpret_cast<const float4 *>(cluster.map_shared_rank(part, rk) + tok * prow + r0);
+                const float4 *src = reinterpret_cast<const float4 *>(recv + (size_t)rk * slot + tok * spitch + r0);
                 const float4 lo = src[0], hi = src[1];
                 v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
             }
-            finish(tok, r0, v);
+            finish(tok, slice * span + r0, v);
         }
-        cluster.sync();  // peers may still be reading this CTA's partials
     }
     TRACE_STAMP(6);
     if (p.independent) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -582,11 +628,12 @@ std::unordered_map<PlanKey, Plan, PlanKeyHash> g_plans;
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared-memory layout for a launch shape; false when it does not fit.
-bool lay_out(Plan &pl, int planes, int ntok, int tokpad, int rwv, int kwv, int lps, int chunks) {
+bool lay_out(Plan &pl, int planes, int ntok, int tokpad, int rwv, int kwv, int s, int lps, int chunks) {
     const int rows = 32 * rwv;
     const size_t stage_bytes = (size_t)rows * 64;
     const size_t xs_bytes = align_up((size_t)planes * ntok * (lps * 24 + 4) * 4, 128);
-    const size_t part_bytes = align_up((size_t)kwv * tokpad * (rows + 4) * 4, 128);
+    // partial sums of the K-slices, and behind them the receive slots of the cluster fold (one per rank)
+    const size_t part_bytes = align_up((size_t)kwv * tokpad * (rows + 4) * 4 + (s > 1 ? (size_t)tokpad * (rows + 4 * s) * 4 : 0), 128);
     const size_t sb_bytes = align_up((size_t)2 * rows * 4, 128);
     const size_t bar_bytes = 1024;  // 2 * 48 + 1 barriers
     size_t off = kWindowHi;
@@ -607,7 +654,7 @@ bool lay_out(Plan &pl, int planes, int ntok, int tokpad, int rwv, int kwv, int l
     pl.ring0_stages = stages0;
     pl.ring1_offset = (int)off;
     off += (size_t)(stages - stages0) * stage_bytes;
-    pl.smem = off < (size_t)kMinSmem ? (size_t)kMinSmem : off;
+    pl.smem = off;
     return true;
 }
 
@@ -631,7 +678,7 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 const int chunks = lps / 4;
                 if (kwv > chunks) continue;                            // a warp without work
                 Plan cand;
-                if (!lay_out(cand, planes, key.ntok, tokpad, rwv, kwv, lps, chunks)) continue;
+                if (!lay_out(cand, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks)) continue;
                 const int rows = 32 * rwv;
                 int64_t row_tiles = 0;
                 for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;

@@ -114,6 +114,8 @@ class Linear(nn.Linear):
         return base
 
     def train(self, mode: bool = True) -> "Linear":
+        if mode and getattr(self, "_t81_float_released", False):
+            raise RuntimeError("this layer's float weight was released at conversion; it can only run in eval mode")
         if mode:
             self.ternary_weight = None
         return super().train(mode)
