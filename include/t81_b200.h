@@ -286,6 +286,23 @@ T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, 
                                           int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
                                           float alpha, float beta, void *stream);
 
+/* Transcoders between the packed-limb layout and the GGUF ternary block formats the reference writes and reads
+ * on the CPU through float arrays (t81/gguf.py:518-662: _quantize_blocks_tq1 / _tq2, _dequantize_blocks_tq1 / _tq2;
+ * payload order t81/gguf.py:665-692): blocks of 256 weights of one row, rows padded with zero trits to whole
+ * blocks, (rows, ceil(cols/256), 54 or 66) bytes.  The trits are carried over exactly in both directions.
+ *   packed_to_tq: a block's fp16 scale is row_scale[row] (1 when row_scale is NULL), or 0 for a block without a
+ *                 non-zero trit — what the reference's absmax gives for weights trit * scale.
+ *   tq_to_packed: writes rows * ceil(cols/48) * 16 bytes and, if block_scale is not NULL, the blocks' scales as
+ *                 fp32 (rows, ceil(cols/256)); a matrix whose blocks share one scale per row can be used by
+ *                 t81b200_gemm_trit directly with that scale as row_scale.
+ * t81b200_tq_bytes gives the size of the block payload (-1 for bad arguments). */
+enum { T81B200_TQ1_0 = 0, T81B200_TQ2_0 = 1 };
+T81B200_API int64_t t81b200_tq_bytes(int format, int64_t rows, int64_t cols);
+T81B200_API int t81b200_packed_to_tq(const uint8_t *packed, const float *row_scale, int64_t rows, int64_t cols, int format,
+                                     uint8_t *blocks, void *stream);
+T81B200_API int t81b200_tq_to_packed(const uint8_t *blocks, int64_t rows, int64_t cols, int format, uint8_t *packed,
+                                     float *block_scale, void *stream);
+
 T81B200_API size_t t81b200_gemm_trit_workspace_bytes(int b_dtype, int layout, int c_dtype, int64_t M,
                                          int64_t N, int64_t K);
 

@@ -194,3 +194,56 @@ def lerp(start, end, weight) -> np.ndarray:
 def addcmul(input, tensor1, tensor2, value: float = 1.0) -> np.ndarray:
     a, t1, t2 = _f32c(input), _f32c(tensor1), _f32c(tensor2)
     return (a + (np.float32(value) * t1) * t2).astype(np.float32)
+
+
+# ---- GGUF ternary block formats (t81/gguf.py:518-662) -------------------------------------------------
+# Blocks of 256 weights of one row; a weight is d * (q - 1) with q = trit + 1 and d an fp16 scale.
+#   TQ2_0, 66 bytes (_quantize_blocks_tq2, :586-600; _dequantize_blocks_tq2, :653-662)
+#   TQ1_0, 54 bytes (_quantize_blocks_tq1, :526-547; _dequantize_blocks_tq1, :603-620)
+# Restated for trits that are already known (no float round trip): a block's scale is the row's scale, or 0
+# when the block has no non-zero trit (the absmax the reference takes of trit * scale).
+
+
+def tq_encode(trits, row_scale, fmt: str) -> np.ndarray:
+    t = np.ascontiguousarray(trits, dtype=np.int8)
+    rows, cols = t.shape
+    bpr = (cols + 255) // 256
+    q = np.ones((rows, bpr * 256), np.uint16)
+    q[:, :cols] = t + 1
+    q = q.reshape(rows * bpr, 256)
+    scale = np.ones(rows, np.float32) if row_scale is None else _f32c(row_scale)
+    d = np.repeat(scale, bpr).reshape(rows * bpr, 1)
+    d = np.where((q != 1).any(axis=1, keepdims=True), d, np.float32(0.0)).astype(np.float16)
+    if fmt == "TQ2_0":
+        g = q.reshape(-1, 2, 4, 32)
+        qs = (g[:, :, 0] | (g[:, :, 1] << 2) | (g[:, :, 2] << 4) | (g[:, :, 3] << 6)).reshape(-1, 64)
+    elif fmt == "TQ1_0":
+        w5 = np.array([81, 27, 9, 3, 1], np.uint16).reshape(1, 5, 1)
+        qs0 = (q[:, :160].reshape(-1, 5, 32) * w5).sum(axis=1)
+        qs1 = (q[:, 160:240].reshape(-1, 5, 16) * w5).sum(axis=1)
+        qh = (q[:, 240:].reshape(-1, 4, 4) * w5[:, :4]).sum(axis=1)
+        v = np.concatenate([qs0, qs1, qh], axis=1).astype(np.uint32)
+        qs = (v * 256 + 242) // 243
+    else:
+        raise ValueError(fmt)
+    out = np.concatenate([qs.astype(np.uint8), d.view(np.uint8).reshape(-1, 2)], axis=1)
+    return out.reshape(rows, bpr, -1)
+
+
+def tq_decode(blocks, rows: int, cols: int, fmt: str):
+    """Returns (trits int8 (rows, cols), block scales float32 (rows, blocks per row))."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(rows, -1, 66 if fmt == "TQ2_0" else 54)
+    bpr = b.shape[1]
+    flat = b.reshape(rows * bpr, -1)
+    d = flat[:, -2:].copy().view(np.float16).astype(np.float32).reshape(rows, bpr)
+    if fmt == "TQ2_0":
+        qs = flat[:, :64].reshape(-1, 2, 1, 32) >> np.array([0, 2, 4, 6], np.uint8).reshape(1, 1, 4, 1)
+        q = np.minimum(qs & 3, 2).reshape(-1, 256)
+    else:
+        p5 = np.array([1, 3, 9, 27, 81], np.uint8).reshape(1, 5, 1)
+        a = (flat[:, :32].reshape(-1, 1, 32) * p5).reshape(-1, 160)            # uint8 arithmetic wraps on purpose
+        c = (flat[:, 32:48].reshape(-1, 1, 16) * p5).reshape(-1, 80)
+        h = (flat[:, 48:52].reshape(-1, 1, 4) * p5[:, :4]).reshape(-1, 16)
+        q = (np.concatenate([a, c, h], axis=1).astype(np.uint16) * 3) >> 8
+    trits = (q.astype(np.int8) - 1).reshape(rows, bpr * 256)[:, :cols]
+    return np.ascontiguousarray(trits), d

@@ -264,3 +264,43 @@ def gemm_trit_grouped(packed, x: torch.Tensor, *, K: int, row_scales=None, biase
             n, arr(packed), arr(scales), arr(bs), arr(outs), (ctypes.c_int64 * n)(*rows), _ptr(x), _dtype_code(x, "x"),
             ldb, _dtype_code(outs[0], "out"), ldc, tokens, K, float(alpha), float(beta), _stream(dev)))
     return outs
+
+
+_TQ = {"TQ1_0": _capi.TQ1_0, "TQ2_0": _capi.TQ2_0}
+
+
+def packed_to_tq(packed: torch.Tensor, rows: int, cols: int, fmt: str = "TQ2_0",
+                 row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed limbs (+ per-row scale) -> GGUF TQ1_0 / TQ2_0 block payload, uint8 (rows, ceil(cols/256), 54 | 66),
+    on the device; the trits are carried over exactly (t81/gguf.py:518-600 without the float round trip)."""
+    _require_cuda(packed, "packed")
+    if fmt not in _TQ:
+        raise ValueError(f"unknown block format {fmt!r}")
+    packed = packed.contiguous()
+    nbytes = _capi.lib.t81b200_tq_bytes(_TQ[fmt], rows, cols)
+    per_block = 66 if fmt == "TQ2_0" else 54
+    out = torch.empty((rows, (cols + 255) // 256, per_block), dtype=torch.uint8, device=packed.device)
+    assert out.numel() == nbytes
+    rs = row_scale
+    if rs is not None and (rs.dtype != torch.float32 or rs.device != packed.device or not rs.is_contiguous()):
+        rs = rs.to(device=packed.device, dtype=torch.float32).contiguous()
+    with torch.cuda.device(packed.device):
+        _capi.check(_capi.lib.t81b200_packed_to_tq(_ptr(packed), _ptr(rs), rows, cols, _TQ[fmt], _ptr(out), _stream(packed.device)))
+    return out
+
+
+def tq_to_packed(blocks: torch.Tensor, rows: int, cols: int, fmt: str = "TQ2_0"):
+    """GGUF TQ1_0 / TQ2_0 block payload -> (packed limbs uint8 (rows, ceil(cols/48), 16), block scales fp32
+    (rows, ceil(cols/256))), on the device."""
+    _require_cuda(blocks, "blocks")
+    if fmt not in _TQ:
+        raise ValueError(f"unknown block format {fmt!r}")
+    blocks = blocks.contiguous()
+    if blocks.numel() != _capi.lib.t81b200_tq_bytes(_TQ[fmt], rows, cols):
+        raise ValueError("block payload size does not match (rows, cols)")
+    packed = torch.empty((rows, k_limbs(cols), 16), dtype=torch.uint8, device=blocks.device)
+    scales = torch.empty((rows, (cols + 255) // 256), dtype=torch.float32, device=blocks.device)
+    with torch.cuda.device(blocks.device):
+        _capi.check(_capi.lib.t81b200_tq_to_packed(_ptr(blocks), rows, cols, _TQ[fmt], _ptr(packed), _ptr(scales),
+                                                   _stream(blocks.device)))
+    return packed, scales
