@@ -286,6 +286,21 @@ T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, 
                                           int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
                                           float alpha, float beta, void *stream);
 
+/* Quantisation-aware-training forward of t81.nn.Linear (t81/nn/linear.py:72-99, t81/qat.py:12-57), the parts
+ * that touch every weight.
+ *   qat_update_scale: candidate = max(max |w|, 1e-6); the first call stores it, later calls store
+ *       max(state[0] * momentum + candidate * (1 - momentum), 1e-6) — _update_training_scale with the reference's
+ *       momentum 0.99.  `state` is 4 floats of device memory owned by the layer, zero before the first call:
+ *       [0] the running scale, [1] and [2] scratch (zero between calls), [3] non-zero once [0] is valid.
+ *   qat_quantize_pack: trit = sign(w / scale) where |clamp(w / scale, -1, 1)| >= threshold, else 0 (the deterministic
+ *       rule of t81/qat.py:12-25; `scale` is read from device memory, e.g. state), packed row-wise into limbs; if
+ *       row_scale is not NULL every entry receives `scale`, so that t81b200_gemm_trit(packed, row_scale, ...) is the
+ *       forward F.linear(x, quantized * scale, bias) without materialising the quantised weight. */
+T81B200_API int t81b200_qat_update_scale(const void *w, int w_dtype, int64_t rows, int64_t cols, int64_t ld, float momentum,
+                                         float *state, void *stream);
+T81B200_API int t81b200_qat_quantize_pack(const void *w, int w_dtype, int64_t rows, int64_t cols, int64_t ld, float threshold,
+                                          const float *scale, uint8_t *packed, float *row_scale, void *stream);
+
 /* Transcoders between the packed-limb layout and the GGUF ternary block formats the reference writes and reads
  * on the CPU through float arrays (t81/gguf.py:518-662: _quantize_blocks_tq1 / _tq2, _dequantize_blocks_tq1 / _tq2;
  * payload order t81/gguf.py:665-692): blocks of 256 weights of one row, rows padded with zero trits to whole

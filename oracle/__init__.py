@@ -247,3 +247,40 @@ def tq_decode(blocks, rows: int, cols: int, fmt: str):
         q = (np.concatenate([a, c, h], axis=1).astype(np.uint16) * 3) >> 8
     trits = (q.astype(np.int8) - 1).reshape(rows, bpr * 256)[:, :cols]
     return np.ascontiguousarray(trits), d
+
+
+# ---- quantisation-aware-training forward (t81/nn/linear.py:72-99, t81/qat.py:12-57) --------------------
+
+
+def qat_update_scale(weight, existing=None, momentum: float = 0.99) -> np.float32:
+    """_update_training_scale: max(max |w|, 1e-6) on the first call, afterwards
+    max(existing * momentum + candidate * (1 - momentum), 1e-6), every operation in float32."""
+    candidate = np.maximum(np.abs(_f32c(weight)).max(), np.float32(1e-6)).astype(np.float32)
+    if existing is None:
+        return candidate
+    combined = np.float32(existing) * np.float32(momentum) + candidate * np.float32(1.0 - momentum)
+    return np.maximum(combined, np.float32(1e-6)).astype(np.float32)
+
+
+def qat_quantize(weight, scale, threshold: float) -> np.ndarray:
+    """_quantize_tensor on weight / scale (deterministic): clamp to [-1, 1], sign where |.| >= threshold."""
+    scaled = _f32c(weight) / np.float32(scale)
+    clamped = np.clip(scaled, np.float32(-1.0), np.float32(1.0))
+    thr = np.float32(max(0.0, min(threshold, 1.0)))
+    return np.where(np.abs(clamped) >= thr, np.sign(clamped), 0).astype(np.int8)
+
+
+def qat_linear(weight, scale, threshold: float, x, bias=None):
+    """F.linear(x, quantized * scale, bias) in float64, and the gradients of sum(y * gy) the reference's autograd
+    yields: returns a function gy -> (y, grad_x, grad_w, grad_b)."""
+    w = _f32c(weight)
+    trits = qat_quantize(w, scale, threshold).astype(np.float64)
+    w_eff = trits * np.float64(scale)
+    xs = np.asarray(x, np.float64)
+    y = xs @ w_eff.T + (0.0 if bias is None else np.asarray(bias, np.float64))
+
+    def grads(gy):
+        gy = np.asarray(gy, np.float64)
+        slope = np.where(np.abs(w / np.float32(scale)) < np.float32(0.5), 2.0, 0.0)  # dorso_round's derivative
+        return y, gy @ w_eff, (gy.T @ xs) * slope, gy.sum(axis=0)
+    return grads

@@ -28,6 +28,7 @@ EXPORTS = (
     "t81b200_copy_columns", "t81b200_gemm_trit_peers", "t81b200_exchange_wait", "t81b200_hint_independent",
     "t81b200_gemm_limb_auto", "t81b200_gemm_trit_auto", "t81b200_elementwise", "t81b200_elementwise_auto",
     "t81b200_gemm_trit_grouped", "t81b200_tq_bytes", "t81b200_packed_to_tq", "t81b200_tq_to_packed",
+    "t81b200_qat_update_scale", "t81b200_qat_quantize_pack",
 )
 TQ1_0, TQ2_0 = 0, 1
 MAX_GROUP = 3       # T81B200_MAX_GROUP
@@ -78,6 +79,8 @@ def _load() -> ctypes.CDLL:
     lib.t81b200_gemm_trit_auto.argtypes = [vp, vp, vp, i64, i64, i64, f32, f32]
     lib.t81b200_elementwise.argtypes = [ci, vp, vp, vp, vp, i64, f32, f32, vp]
     lib.t81b200_elementwise_auto.argtypes = [ci, vp, vp, vp, vp, i64, f32, f32]
+    lib.t81b200_qat_update_scale.argtypes = [vp, ci, i64, i64, i64, f32, vp, vp]
+    lib.t81b200_qat_quantize_pack.argtypes = [vp, ci, i64, i64, i64, f32, vp, vp, vp, vp]
     lib.t81b200_tq_bytes.argtypes = [ci, i64, i64]
     lib.t81b200_tq_bytes.restype = i64
     lib.t81b200_packed_to_tq.argtypes = [vp, vp, i64, i64, ci, vp, vp]

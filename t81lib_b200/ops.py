@@ -304,3 +304,35 @@ def tq_to_packed(blocks: torch.Tensor, rows: int, cols: int, fmt: str = "TQ2_0")
         _capi.check(_capi.lib.t81b200_tq_to_packed(_ptr(blocks), rows, cols, _TQ[fmt], _ptr(packed), _ptr(scales),
                                                    _stream(blocks.device)))
     return packed, scales
+
+
+def qat_update_scale(weight: torch.Tensor, state: torch.Tensor, momentum: float = 0.99) -> torch.Tensor:
+    """Running absmax scale of a QAT layer on the device (t81/nn/linear.py:82-99).  ``state`` is the layer's
+    4-float CUDA buffer (zeros before the first call); returns the one-element view that holds the scale."""
+    _require_cuda(weight, "weight")
+    if weight.ndim != 2 or weight.stride(1) != 1:
+        raise ValueError("qat_update_scale expects a 2D weight with unit inner stride")
+    if state.dtype != torch.float32 or state.numel() != 4 or state.device != weight.device:
+        raise ValueError("state must be 4 float32 values on the weight's device")
+    rows, cols = weight.shape
+    with torch.cuda.device(weight.device):
+        _capi.check(_capi.lib.t81b200_qat_update_scale(_ptr(weight), _dtype_code(weight, "weight"), rows, cols,
+                                                       weight.stride(0) if rows > 1 else max(cols, 1), float(momentum),
+                                                       _ptr(state), _stream(weight.device)))
+    return state[:1]
+
+
+def qat_quantize_pack(weight: torch.Tensor, threshold: float, scale: torch.Tensor):
+    """Quantise ``weight / scale`` with the training rule (t81/qat.py:12-25, deterministic) and pack it; ``scale`` is a
+    one-element CUDA tensor.  Returns (packed limbs, row_scale filled with the scale)."""
+    _require_cuda(weight, "weight")
+    if weight.ndim != 2 or weight.stride(1) != 1:
+        raise ValueError("qat_quantize_pack expects a 2D weight with unit inner stride")
+    rows, cols = weight.shape
+    packed = torch.empty((rows, k_limbs(cols), 16), dtype=torch.uint8, device=weight.device)
+    row_scale = torch.empty(rows, dtype=torch.float32, device=weight.device)
+    with torch.cuda.device(weight.device):
+        _capi.check(_capi.lib.t81b200_qat_quantize_pack(_ptr(weight), _dtype_code(weight, "weight"), rows, cols,
+                                                        weight.stride(0) if rows > 1 else max(cols, 1), float(threshold),
+                                                        _ptr(scale), _ptr(packed), _ptr(row_scale), _stream(weight.device)))
+    return packed, row_scale
