@@ -61,14 +61,13 @@ __global__ void __launch_bounds__(kBlock) packed_to_tq_kernel(const uint8_t *__r
             out[i] = (uint8_t)((v * 256 + 242) / 243);
         }
     }
-    if (i == 0) {
-        // the scale of a block with no non-zero trit is 0, like the absmax of an all-zero block
+    if (i >= kBlock - 2) {
+        // the scale of a block with no non-zero trit is 0, like the absmax of an all-zero block; the last two
+        // threads store its fp16 bits, low byte first
         const float d = nonzero ? (row_scale ? row_scale[row] : 1.0f) : 0.0f;
-        const __half h = __float2half_rn(d);
-        const uint16_t bits = *reinterpret_cast<const uint16_t *>(&h);
-        const int at = block_bytes(format) - 2;
-        out[at] = (uint8_t)(bits & 0xFF);
-        out[at + 1] = (uint8_t)(bits >> 8);
+        const unsigned int bits = __half_as_ushort(__float2half_rn(d));
+        const int which = i - (kBlock - 2);
+        out[block_bytes(format) - 2 + which] = (uint8_t)((bits >> (8 * which)) & 0xFFu);
     }
 }
 
@@ -109,7 +108,7 @@ __global__ void __launch_bounds__(256) tq_to_packed_kernel(const uint8_t *__rest
     if (block_scale && n < blocks_per_row) {
         const uint8_t *b = rblocks + n * bb + bb - 2;
         const uint16_t bits = (uint16_t)(b[0] | (b[1] << 8));
-        block_scale[row * blocks_per_row + n] = __half2float(*reinterpret_cast<const __half *>(&bits));
+        block_scale[row * blocks_per_row + n] = __half2float(__ushort_as_half(bits));
     }
 }
 
