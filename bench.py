@@ -464,7 +464,9 @@ def run_ours(args):
         line["clocks"] = clocks.summary()
 
     # ---- end to end through the public API (t81lib_b200.nn.Linear), host buffers in and out
-    if world == 1:
+    if args.brief:
+        pass
+    elif world == 1:
         line["e2e"] = e2e_public_api(torch, dev, Linear, layers, args)
         line["quantize_pack"] = quantize_pack_line(torch, dev, ops, pk)
         line["configs"] = small_configs(torch, dev, ops, pk)
@@ -876,6 +878,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--brief", action="store_true",
+                    help="timed region only: no end-to-end pass, no small configurations, no CPU baseline (profiling runs)")
     args = ap.parse_args()
     if args.kernel == "sweep":
         run_sweep(args)

@@ -125,17 +125,23 @@ void t81o_pack_dense_matrix(const float *w, int64_t rows, int64_t cols, int64_t 
     parallel_rows(rows, pack_fixed_rows, &c);
 }
 
+static float absmean_group_sum(const float *row, int64_t g, int64_t cols) {
+    float v[4];
+    for (int c = 0; c < 4; ++c) v[c] = 4 * g + c < cols ? fabsf(row[4 * g + c]) : 0.0f;
+    volatile float lo = v[0] + v[1], hi = v[2] + v[3]; /* fp32, each sum rounded */
+    volatile float s = lo + hi;
+    return s;
+}
+
 static float absmean_row_scale(const float *row, int64_t cols) {
+    const int64_t groups = (cols + 3) / 4, words = (groups + 2) / 3;
     double part[T81O_ABSMEAN_LANES];
-    for (int l = 0; l < T81O_ABSMEAN_LANES; ++l) {
+    for (int tau = 0; tau < T81O_ABSMEAN_LANES; ++tau) {
         double s = 0.0;
-        for (int64_t i = 0;; ++i) {
-            int64_t base = 4 * ((int64_t)l + T81O_ABSMEAN_LANES * i);
-            if (base >= cols) break;
-            for (int c = 0; c < 4; ++c)
-                if (base + c < cols) s += (double)fabsf(row[base + c]);
-        }
-        part[l] = s;
+        for (int64_t q = tau; q < words; q += T81O_ABSMEAN_LANES)
+            for (int j = 0; j < 3; ++j)
+                if (3 * q + j < groups) s += (double)absmean_group_sum(row, 3 * q + j, cols);
+        part[tau] = s;
     }
     double grp[T81O_ABSMEAN_LANES / 32];
     for (int g = 0; g < T81O_ABSMEAN_LANES / 32; ++g) {

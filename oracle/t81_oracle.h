@@ -30,7 +30,7 @@ extern "C" {
 
 #define T81O_TRITS_PER_LIMB 48
 #define T81O_BYTES_PER_LIMB 16
-#define T81O_ABSMEAN_LANES 256 /* partial sums of the absmean reduction */
+#define T81O_ABSMEAN_LANES 128 /* partial sums of the absmean reduction */
 
 /* python/bindings.cpp:405-414 — clamp to [-1,1], inclusive compares in fp32. */
 int8_t t81o_quantize_trit(float value, float threshold);
@@ -52,11 +52,12 @@ void t81o_pack_dense_matrix(const float *w, int64_t rows, int64_t cols, int64_t 
 /* Rule "absmean" (no reference counterpart; shaped after quantize_row_tq1_0,
  * src/t81/core/gguf_quants.h:55-64,116-144, with the row mean of |w| in place
  * of the row absmax):
- *   partial[l] = sum over i (ascending), c = 0..3 of double(|w[r, 4*(l + 256*i) + c]|),
- *                l = 0..255, elements past cols skipped;
- *   the 256 partials are folded by halving trees: inside each group of 32
- *   consecutive partials (offsets 16,8,4,2,1: v[j] += v[j+off]), then over the
- *   8 group sums (offsets 4,2,1);
+ *   group sum g(j) = fp32 (|w[r,4j]| + |w[r,4j+1]|) + (|w[r,4j+2]| + |w[r,4j+3]|), each of the three additions
+ *                rounded to fp32, elements past cols counting 0;
+ *   partial[tau], tau = 0..127 = double sum, in this order, of g(3q), g(3q+1), g(3q+2) for q = tau, tau + 128,
+ *                tau + 256, ... (q numbers the 32-bit words of the packed row: 12 weights each);
+ *   the 128 partials are folded by halving trees: inside each group of 32 consecutive partials (offsets
+ *   16,8,4,2,1: v[j] += v[j+off]), then over the 4 group sums (offsets 2,1);
  *   s_r = float(total / double(cols));  inv = s_r > 0 ? 1.0f / s_r : 0.0f;
  *   trit = quantize_trit(w * inv, threshold)   (one fp32 multiply).
  * row_scale[r] = s_r. */

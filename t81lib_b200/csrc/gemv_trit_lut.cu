@@ -683,19 +683,20 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 int64_t row_tiles = 0;
                 for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;
                 // Cost model, fitted to a sweep of every launch shape over the Llama- and Phi-shaped layers (mean
-                // regret 2.5 %): a warp needs about a microsecond per chunk of 32 rows whatever shares its
-                // scheduler, up to four warps per scheduler; every CTA pulls its own copy of its slice of the
-                // activations out of L2, which delivers about 3 TB/s when all CTAs ask for the same lines at once;
-                // the longer of the two bounds the CTA; a launch costs 2 us, a cluster's fold 1 us more.
-                // Clusters must fit inside a GPC: fewer CTAs are co-resident than there are SMs.
+                // regret 3 %): a warp needs about 0.6 us per chunk of 32 rows whatever shares its scheduler, up to
+                // three warps per scheduler; every CTA pulls its own copy of its slice of the activations out of
+                // L2, which delivers about 5 TB/s when all CTAs ask for the same lines at once; the longer of the
+                // two bounds the CTA and a fifth of the shorter is not hidden; a launch costs 1.5 us, a cluster's
+                // fold 0.5 to 0.7 us more.  Clusters must fit inside a GPC: fewer CTAs are co-resident than SMs.
                 const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : sms - 20);
                 const double waves = ceil((double)row_tiles * s / wave_ctas);
-                const double warps_per_sched = ceil(rwv * kwv / 4.0);
-                const double chunks_per_warp = ceil((double)chunks / kwv);
-                const double work = chunks_per_warp * 1.0e-6 * (1.0 + 0.6 * (planes * (tokpad / 8) - 1)) *
-                                    (warps_per_sched > 4.0 ? warps_per_sched / 4.0 : 1.0);
-                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / 3.0e12;
-                const double t = waves * (2.0e-6 + (s > 1 ? 1.0e-6 : 0.0) + (work > x_fetch ? work : x_fetch));
+                const double warps_per_sched = rwv * kwv / 4.0;
+                const double chunks_per_warp = 0.3 * ceil((double)chunks / kwv) + 0.7 * (double)chunks / kwv;
+                const double work = chunks_per_warp * 0.6e-6 * (1.0 + 0.4 * (planes * (tokpad / 8) - 1)) *
+                                    (warps_per_sched > 3.0 ? warps_per_sched / 3.0 : 1.0);
+                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / 5.0e12;
+                const double t = waves * (1.5e-6 + (s == 2 ? 0.7e-6 : (s == 4 ? 0.5e-6 : 0.0)) +
+                                          (work > x_fetch ? work + 0.2 * x_fetch : x_fetch + 0.2 * work));
                 if (t < best_t) {
                     best_t = t;
                     best = cand;

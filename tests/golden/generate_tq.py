@@ -17,7 +17,8 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+    "T81_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
 WANTED = {"_round_away_from_zero", "_quantize_trits", "_quantize_blocks_tq1", "_quantize_blocks_tq2",
           "_dequantize_blocks_tq1", "_dequantize_blocks_tq2"}
 

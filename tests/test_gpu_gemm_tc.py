@@ -78,7 +78,7 @@ def test_tc_gemm_alpha_beta_and_column_slice(dev):
 
 
 def test_prefill_shape_linearity_at_full_size(dev):
-    """BASELINE config 4 size (M = 2048 tokens, 3072 -> 9216): checked through linearity,
+    """A 2048-token prefill of the Phi-3-mini qkv layer (3072 -> 9216): checked through linearity,
     y(a*x1 + x2) == a*y(x1) + y(x2), and a sampled comparison with the oracle."""
     from t81lib_b200 import _capi, ops
     gen = torch.Generator(device="cpu").manual_seed(4)

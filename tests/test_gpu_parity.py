@@ -90,7 +90,7 @@ def test_pack_strided_unaligned_and_half_inputs(dev):
 
 
 def test_pack_config2_full_size_properties(dev):
-    """BASELINE config 2 at full size: 4096x4096 N(0, 0.02^2), threshold 0.45."""
+    """Quantise + pack at full size: 4096x4096 N(0, 0.02^2), threshold 0.45."""
     from t81lib_b200 import ops
     gen = torch.Generator(device="cpu").manual_seed(2)
     w = (torch.randn(4096, 4096, generator=gen) * 0.02)
@@ -224,7 +224,7 @@ def test_trit_ignores_trits_beyond_k(dev):
 
 
 def test_config1_gemm_ternary_trit_mode(dev):
-    """BASELINE config 1: A 512x512 uniform trits packed by the reference packer rule,
+    """gemm_ternary at 512x512x256: A 512x512 uniform trits packed by the reference packer rule,
     B 512x256 fp32 N(0,1), C N(0,1), alpha 1, beta 0.5, fp32 accumulate."""
     from t81lib_b200 import t81lib
     rng = np.random.default_rng(1)

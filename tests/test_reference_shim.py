@@ -17,7 +17,7 @@ import oracle
 from oracle import ref as oracle_ref
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE = os.environ.get("T81_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("T81_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))  # beside the repository
 DRIVER = os.path.join(oracle_ref.cuda_dir(), "ref_cuda_driver")
 
 
