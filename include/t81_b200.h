@@ -55,10 +55,11 @@ enum {
 enum { T81B200_F32 = 0, T81B200_BF16 = 1, T81B200_F16 = 2 };
 
 /* Quantiser rule. FIXED is the reference rule (python/bindings.cpp:405-414,
- * t81/torch/__init__.py:44-50).  ABSMEAN divides each row by the mean of |w| of
- * that row first and returns that mean as the row's scale; the reference has no
- * such rule, it is shaped after quantize_row_tq1_0 (src/t81/core/gguf_quants.h:116-144)
- * with the mean in place of the absmax. */
+ * t81/torch/__init__.py:44-50).  ABSMEAN compares each weight with threshold times
+ * the mean of |w| of its row (-1 at or below minus that cut, +1 at or above it) and
+ * returns the mean as the row's scale; the reference has no such rule, it is shaped
+ * after quantize_row_tq1_0 (src/t81/core/gguf_quants.h:116-144) with the mean in
+ * place of the absmax. */
 enum { T81B200_RULE_FIXED = 0, T81B200_RULE_ABSMEAN = 1 };
 
 /* Operand layout of the dense side of t81b200_gemm_trit.
@@ -210,7 +211,8 @@ T81B200_API int t81b200_elementwise_auto(int op, const float *a, const float *b,
  * 1..4 = a bounded wait inside the tensor-core kernel expired (producer, MMA issuer,
  * epilogue, converter), 5..6 = inside the streaming kernel (producer, consumer), 7 = a wait
  * on the exchange flags of a sharded call, 8 = the streaming kernel found dynamic shared memory
- * starting above the address its tables were laid out for; that launch's output is invalid.  The kernel never spins forever:
+ * starting above the address its tables were laid out for, 9..10 = a wait inside the streaming quantise + pack
+ * kernel (producer, consumer); that launch's output is invalid.  The kernels never spin forever:
  * every wait has an iteration limit after which it records the code, releases its
  * tensor memory and returns.  Reading the word synchronises the device; `reset`
  * non-zero clears it.  No counterpart in the reference (its CUDA path has no

@@ -134,14 +134,14 @@ static float absmean_group_sum(const float *row, int64_t g, int64_t cols) {
 }
 
 static float absmean_row_scale(const float *row, int64_t cols) {
-    const int64_t groups = (cols + 3) / 4, words = (groups + 2) / 3;
+    const int64_t groups = (cols + 3) / 4;
     double part[T81O_ABSMEAN_LANES];
-    for (int tau = 0; tau < T81O_ABSMEAN_LANES; ++tau) {
-        double s = 0.0;
-        for (int64_t q = tau; q < words; q += T81O_ABSMEAN_LANES)
-            for (int j = 0; j < 3; ++j)
-                if (3 * q + j < groups) s += (double)absmean_group_sum(row, 3 * q + j, cols);
-        part[tau] = s;
+    for (int i = 0; i < T81O_ABSMEAN_LANES; ++i) part[i] = 0.0;
+    /* chunks of 96 groups go round the four blocks of 32 partials; inside a chunk group j adds to partial j % 32 */
+    for (int64_t g = 0; g < groups; ++g) {
+        const int64_t chunk = g / 96;
+        const int idx = (int)(chunk % (T81O_ABSMEAN_LANES / 32)) * 32 + (int)((g % 96) % 32);
+        part[idx] += (double)absmean_group_sum(row, g, cols);
     }
     double grp[T81O_ABSMEAN_LANES / 32];
     for (int g = 0; g < T81O_ABSMEAN_LANES / 32; ++g) {
@@ -152,7 +152,9 @@ static float absmean_row_scale(const float *row, int64_t cols) {
     }
     for (int off = T81O_ABSMEAN_LANES / 64; off >= 1; off >>= 1)
         for (int j = 0; j < off; ++j) grp[j] += grp[j + off];
-    return (float)(grp[0] / (double)cols);
+    volatile float total = (float)grp[0], n = (float)cols;
+    volatile float mean = total / n; /* fp32 division of the two rounded values */
+    return mean;
 }
 
 static void pack_absmean_rows(int64_t lo, int64_t hi, void *p) {
@@ -163,18 +165,15 @@ static void pack_absmean_rows(int64_t lo, int64_t hi, void *p) {
     for (int64_t r = lo; r < hi; ++r) {
         const float *row = cx->w + r * cx->ld;
         const float s = cols > 0 ? absmean_row_scale(row, cols) : 0.0f;
-        const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+        volatile float product = threshold * s; /* one fp32 multiply, rounded */
+        const float cut = s > 0.0f ? product : INFINITY; /* a mean that is 0 or NaN: zero trits */
         if (cx->row_scale) cx->row_scale[r] = s;
         for (int64_t l = 0; l < kl; ++l) {
             int8_t t[T81O_TRITS_PER_LIMB];
             for (int i = 0; i < 48; ++i) {
                 int64_t c = l * 48 + i;
-                if (c < cols) {
-                    volatile float scaled = row[c] * inv; /* one fp32 multiply, rounded */
-                    t[i] = t81o_quantize_trit(scaled, threshold);
-                } else {
-                    t[i] = 0;
-                }
+                t[i] = 0;
+                if (c < cols) t[i] = row[c] <= -cut ? -1 : (row[c] >= cut ? 1 : 0);
             }
             pack_limb(t, packed + (r * kl + l) * 16);
         }

@@ -54,12 +54,12 @@ void t81o_pack_dense_matrix(const float *w, int64_t rows, int64_t cols, int64_t 
  * of the row absmax):
  *   group sum g(j) = fp32 (|w[r,4j]| + |w[r,4j+1]|) + (|w[r,4j+2]| + |w[r,4j+3]|), each of the three additions
  *                rounded to fp32, elements past cols counting 0;
- *   partial[tau], tau = 0..127 = double sum, in this order, of g(3q), g(3q+1), g(3q+2) for q = tau, tau + 128,
- *                tau + 256, ... (q numbers the 32-bit words of the packed row: 12 weights each);
+ *   partial[i], i = 0..127 = double sum, in increasing j, of the g(j) with ((j / 96) % 4) * 32 + (j % 96) % 32 == i
+ *                (chunks of 96 groups go round four blocks of 32 partials; inside a chunk group j feeds j % 32);
  *   the 128 partials are folded by halving trees: inside each group of 32 consecutive partials (offsets
  *   16,8,4,2,1: v[j] += v[j+off]), then over the 4 group sums (offsets 2,1);
- *   s_r = float(total / double(cols));  inv = s_r > 0 ? 1.0f / s_r : 0.0f;
- *   trit = quantize_trit(w * inv, threshold)   (one fp32 multiply).
+ *   s_r = float(total) / float(cols), an fp32 division;  cut = s_r > 0 ? threshold * s_r (one fp32 multiply) : +inf;
+ *   trit = w <= -cut ? -1 : (w >= cut ? +1 : 0)   (the weight itself is compared: no per-weight arithmetic).
  * row_scale[r] = s_r. */
 void t81o_pack_dense_matrix_absmean(const float *w, int64_t rows, int64_t cols, int64_t ld,
                                     float threshold, uint8_t *packed, float *row_scale);

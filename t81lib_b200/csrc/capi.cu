@@ -83,6 +83,7 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
 int gemm_trit_tc_status(int reset);
 int gemv_trit_status(int reset);
 int gemv_trit_lut_status(int reset);
+int quantize_pack_status(int reset);
 int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
                          void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
                          int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx);
@@ -96,7 +97,8 @@ extern "C" int t81b200_kernel_status(int reset) {
     const int tc = gemm_trit_tc_status(reset);
     const int gv = gemv_trit_status(reset);
     const int lut = gemv_trit_lut_status(reset);
-    return tc != 0 ? tc : (gv != 0 ? gv : lut);
+    const int qp = quantize_pack_status(reset);
+    return tc != 0 ? tc : (gv != 0 ? gv : (lut != 0 ? lut : qp));
 }
 
 extern "C" int t81b200_copy_columns(void *dst, int64_t dst_pitch, const void *src, int64_t src_pitch,

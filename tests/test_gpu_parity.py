@@ -73,6 +73,46 @@ def test_pack_matches_oracle(dev, rows, cols, rule):
     assert np.array_equal(packed.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("rows,cols", [(296, 4), (300, 100), (333, 4096), (297, 4608), (298, 4612), (300, 14336), (1000, 384)])
+@pytest.mark.parametrize("rule", ["fixed", "absmean"])
+def test_pack_streaming_form_matches_oracle(dev, rows, cols, rule):
+    """Matrices of many 16-byte-multiple rows take the kernel that streams whole rows through a shared-memory ring."""
+    from t81lib_b200 import _capi, ops
+    rng = np.random.default_rng(rows * 7 + cols)
+    sigma = 0.5 if rule == "fixed" else 0.02
+    w = rng.normal(0, sigma, (rows, cols)).astype(np.float32)
+    w[2] = 0.0
+    w[5, ::3] = np.nan  # NaN quantises to 0 and poisons an absmean row scale like the oracle's
+    pack = oracle.pack_dense_matrix if rule == "fixed" else oracle.pack_dense_matrix_absmean
+    clean = rng.normal(0, sigma, (rows, cols)).astype(np.float32)  # threshold 0: no zeros (the rule for a zero is the Python layer's)
+    for thr, m in ((0.45, w), (1.0, w), (0.001, w), (0.0, clean)):
+        packed, scale = ops.quantize_pack(cuda(m, dev), thr, rule)
+        want = pack(m, thr)
+        if rule == "absmean":
+            want, want_scale = want
+            assert np.array_equal(scale.cpu().numpy(), want_scale, equal_nan=True)
+        assert np.array_equal(packed.cpu().numpy(), want), thr
+    assert _capi.kernel_status(reset=True) == 0
+
+
+def test_pack_streaming_form_half_inputs_and_padded_rows(dev):
+    from t81lib_b200 import _capi, ops
+    rng = np.random.default_rng(5)
+    big = rng.normal(0, 0.02, (400, 1040)).astype(np.float32)
+    t = cuda(big, dev)
+    for dt in (torch.bfloat16, torch.float16):
+        h = t.to(dt)
+        for view in (h, h[:, 8:1032], h[:, :1000]):  # whole rows; 16-byte aligned view with a leading dimension; 2000-byte rows
+            packed, scale = ops.quantize_pack(view, 0.45, "absmean")
+            want, want_scale = oracle.pack_dense_matrix_absmean(np.ascontiguousarray(view.float().cpu().numpy()), 0.45)
+            assert np.array_equal(packed.cpu().numpy(), want) and np.array_equal(scale.cpu().numpy(), want_scale)
+    view = t[:, 4:1028]
+    packed, scale = ops.quantize_pack(view, 0.45, "absmean")
+    want, want_scale = oracle.pack_dense_matrix_absmean(np.ascontiguousarray(big[:, 4:1028]), 0.45)
+    assert np.array_equal(packed.cpu().numpy(), want) and np.array_equal(scale.cpu().numpy(), want_scale)
+    assert _capi.kernel_status(reset=True) == 0
+
+
 def test_pack_strided_unaligned_and_half_inputs(dev):
     from t81lib_b200 import ops
     rng = np.random.default_rng(11)
@@ -329,15 +369,16 @@ def test_ternary_tensor_surface(dev):
     assert ternary.dtype is t81_torch.trit and tuple(ternary.shape) == (3, 16)
     assert repr(ternary) == "TernaryTensor(shape=(3, 16), trits_per_row=16)"
     assert np.array_equal(ternary.packed.cpu().numpy(), oracle.pack_dense_matrix(weight.numpy(), 0.45))
-    rhs = torch.randn(16, 4, dtype=torch.float32)
+    rhs = torch.randn(16, 4, dtype=torch.float32, generator=torch.Generator().manual_seed(16))
     out = torch.matmul(ternary, rhs)
     assert out.shape == (3, 4) and out.device.type == "cpu"  # result returns to the input's device
     trits = oracle.quantize_to_trits(weight.numpy(), 0.45).astype(np.float32)
-    assert rel_err(out.numpy(), trits @ rhs.numpy()) < 1e-5
+    # fp32 activations reach the decode-sized kernel as two bf16 planes (16 mantissa bits): 1e-4 here, 1e-3 allowed
+    assert rel_err(out.numpy(), trits @ rhs.numpy()) < 1e-4
     out = torch.mm(ternary, rhs.to(dev))
     assert out.device == dev
     y = ternary.matmul_input(rhs.t().contiguous().to(dev))
-    assert y.shape == (4, 3) and rel_err(y.cpu().numpy(), (trits @ rhs.numpy()).T) < 1e-5
+    assert y.shape == (4, 3) and rel_err(y.cpu().numpy(), (trits @ rhs.numpy()).T) < 1e-4
     with pytest.raises(ValueError, match="only support 2D"):
         t81_torch.TernaryTensor.from_float(torch.zeros(2, 2, 2))
     with pytest.raises(ValueError, match="expect 2D activations"):

@@ -102,10 +102,11 @@ def test_absmean_rule_definition():
     packed, scale = oracle.pack_dense_matrix_absmean(w, 0.45)
     np.testing.assert_allclose(scale, np.abs(w).astype(np.float64).mean(axis=1).astype(np.float32), rtol=2e-7)
     assert scale[5] == 0.0
+    trits = oracle.unpack_packed_limbs(packed, 6, 1000)
     for r in range(6):
-        inv = np.float32(1.0) / scale[r] if scale[r] > 0 else np.float32(0.0)
-        want = oracle.pack_dense_matrix((w[r:r + 1] * inv).astype(np.float32), 0.45)
-        assert np.array_equal(packed[r:r + 1], want)
+        cut = np.float32(0.45) * scale[r] if scale[r] > 0 else np.float32(np.inf)
+        want = np.where(w[r] <= -cut, -1, np.where(w[r] >= cut, 1, 0))
+        assert np.array_equal(trits[r], want)
     # thread count does not change results
     oracle.set_num_threads(4)
     p4, s4 = oracle.pack_dense_matrix_absmean(w, 0.45)
