@@ -271,6 +271,9 @@ def run_ours(args):
         return name, hi - lo, in_f, packed[lo:hi], scale[lo:hi]
 
     prefill_mods = [[shard(m) for m in mods] for mods in layers]
+    # decode-sized products read the decode-stream layout (made once per weight, like the packing itself)
+    use_t2 = args.decode_layout == "t2"
+    t2 = [{m[0]: ops.pack_t2(m[3], m[1], m[2]) for m in mods} for mods in layers] if use_t2 else None
 
     # Prefill with N > 1: every GEMM computes this rank's output features and writes them into their
     # columns of its own full-width result AND of every peer's (TMA stores over NVLink from the kernel's
@@ -301,10 +304,13 @@ def run_ours(args):
         # fence, one flag flight over NVLink, one poll), more than the rows a rank would save
         # k, v read what q reads and up reads what gate reads: they need not wait for that predecessor
         # (the decoder block's own data flow; every other Linear runs behind the one before it)
-        for mods in layers:
+        for li, mods in enumerate(layers):
             for name, out_f, in_f, packed, scale in mods:
                 with ops.independent_of_previous() if name in INDEPENDENT else contextlib.nullcontext():
-                    ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_out[name])
+                    if use_t2:
+                        ops.gemm_trit_t2([t2[li][name]], [out_f], xd_in[in_f], K=in_f, row_scales=[scale], outs=[yd_out[name]])
+                    else:
+                        ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_out[name])
 
     # The same step with the Linears that share an input in ONE launch each (q/k/v, gate/up): 4 launches per
     # block instead of 7, through the additive grouped entry point.  Reported beside the per-Linear figure.
@@ -319,16 +325,19 @@ def run_ours(args):
         return outs
 
     def decode_step_grouped():
-        for mods in layers:
+        for li, mods in enumerate(layers):
             by = {m[0]: m for m in mods}
             for names in GROUPS:
                 ms = [by[n] for n in names]
                 in_f = ms[0][2]
-                if len(ms) == 1:
+                outs = [yd_out[names[0]]] if len(ms) == 1 else split(ydg_out["qkv" if names[0] == "q" else "gate_up"], [m[1] for m in ms])
+                if use_t2:
+                    ops.gemm_trit_t2([t2[li][n] for n in names], [m[1] for m in ms], xd_in[in_f], K=in_f,
+                                     row_scales=[m[4] for m in ms], outs=outs)
+                elif len(ms) == 1:
                     name, out_f, _, packed, scale = ms[0]
                     ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_out[name])
                 else:
-                    outs = split(ydg_out["qkv" if names[0] == "q" else "gate_up"], [m[1] for m in ms])
                     ops.gemm_trit_grouped([m[3] for m in ms], xd_in[in_f], K=in_f, row_scales=[m[4] for m in ms], outs=outs)
 
     # the decode step is launch-bound: capture it once in a CUDA graph
@@ -403,8 +412,11 @@ def run_ours(args):
             "kernel": "gemm_trit_tc_kernel", "share_of_step": pre_ms / (pre_ms + dec_ms),
             "note": "prefill phase: 224 launches per step, includes launch gaps" + ("; includes the exchange" if world > 1 else "")}
     # ---- decode: algorithmic bytes of the streaming kernel (the dominant kernel by time)
-    packed_bytes = sum(m[3].numel() for mods in layers for m in mods)  # decode runs whole on every rank
-    bytes_decode = packed_bytes + sum(4 * m[1] + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
+    # weight bytes the decode kernel streams: the decode-stream layout (0.25 byte per trit) or the limbs (0.33)
+    limb_bytes = sum(m[3].numel() for mods in layers for m in mods)  # decode runs whole on every rank
+    packed_bytes = sum(t.numel() for d in t2 for t in d.values()) if use_t2 else limb_bytes
+    other_bytes = sum(4 * m[1] + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
+    bytes_decode = packed_bytes + other_bytes
     n_launch = LAYERS * len(LINEARS)
     gbs = bytes_decode * DECODE / (dec_ms * 1e-3) / 1e9
     # DRAM traffic per launch: the ncu capture of this kernel on the 14336 x 4096 layer reads exactly the packed
@@ -414,6 +426,11 @@ def run_ours(args):
             "traffic_note": "bytes per average launch; dram__bytes measured by ncu on one shape equals the algorithmic bytes there",
             "peak_source": pk["source"] + " (copy bandwidth)", "kernel": "gemv_trit_lut_kernel", "tokens": dtok,
             "algorithmic_bytes_per_launch": bytes_decode / n_launch, "us_per_launch": dec_ms * 1e3 / (DECODE * n_launch),
+            "weight_layout": "decode-stream layout (2 bits per trit, made once per weight)" if use_t2 else "packed limbs",
+            "reference_layout_equivalent": {"bytes_per_launch": (limb_bytes + other_bytes) / n_launch,
+                                            "achieved": (limb_bytes + other_bytes) * DECODE / (dec_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                            "frac": (limb_bytes + other_bytes) * DECODE / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                                            "note": "the same time against the bytes the limb layout would have streamed"},
             "cuda_graph": graph is not None, "share_of_step": dec_ms / (pre_ms + dec_ms),
             "note": "decode phase: 224 launches per step (one per Linear), includes launch gaps" + ("; whole on every rank" if world > 1 else "")}
 
@@ -453,7 +470,7 @@ def run_ours(args):
     line["decode_grouped"] = {"launches_per_step": LAYERS * len(GROUPS), "decode_ms": gdec_ms, "achieved": ggbs, "unit": "GB/s",
                               "frac": ggbs / pk["hbm_gbs"], "frac_of_nominal": ggbs / NOMINAL_HBM_GBS,
                               "tokens_per_s_with_this_decode": job_tokens / ((pre_ms + gdec_ms) * 1e-3),
-                              "api": "t81b200_gemm_trit_grouped: q/k/v and gate/up in one launch each"}
+                              "api": ("t81b200_gemm_trit_t2" if use_t2 else "t81b200_gemm_trit_grouped") + ": q/k/v and gate/up in one launch each"}
     assert _capi.kernel_status(reset=True) == 0, "a kernel reported a timed-out wait"
 
     # ---- N > 1: an un-timed check that the exchange that produced these numbers is right on every rank
@@ -711,10 +728,22 @@ def small_configs(torch, dev, ops, pk):
         w = torch.randn(rows, k, device=dev, generator=gen) * 0.02
         mats = [ops.quantize_pack(w, THRESHOLD, "absmean") for _ in range(copies)]
         bias = torch.randn(rows, device=dev, generator=gen) * 0.01
+        t2s = None
         for tok in (1, 4, 16, 2048):
             x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
             y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
             use = mats if tok <= 16 else mats[:4]
+            if tok <= 16:  # decode-sized: the decode-stream layout of the same weights
+                if t2s is None:
+                    t2s = [ops.pack_t2(m[0], rows, k) for m in mats]
+                us = _graph_time(torch, stream, [lambda m=m, t=t: ops.gemm_trit_t2([t], [rows], x, K=k, row_scales=[m[1]], biases=[bias], outs=[y])
+                                                for m, t in zip(mats, t2s)])
+                alg = t2s[0].numel() + 8 * rows + 2 * tok * k + 2 * tok * rows
+                ref_alg = nbytes + 8 * rows + 2 * tok * k + 2 * tok * rows
+                decode.append({"layer": name, "rows": rows, "k": k, "tokens": tok, "us": us, "gbs": alg / us / 1e3,
+                               "frac": alg / us / 1e3 / pk["hbm_gbs"], "frac_of_nominal": alg / us / 1e3 / NOMINAL_HBM_GBS,
+                               "reference_layout_equivalent_gbs": ref_alg / us / 1e3})
+                continue
             us = _graph_time(torch, stream, [lambda m=m: ops.gemm_trit(m[0], x, M=rows, K=k, layout="nk", row_scale=m[1], bias=bias, C=y)
                                             for m in use])
             if tok <= 16:
@@ -726,7 +755,8 @@ def small_configs(torch, dev, ops, pk):
                 prefill.append({"layer": name, "rows": rows, "k": k, "tokens": tok, "us": us, "tflops": tfl,
                                 "frac_of_burst": tfl / pk["bf16_tflops"], "frac_of_nominal": tfl / NOMINAL_BF16_TFLOPS})
         del mats, w
-    out["phi3_decode_sweep"] = {"peak_gbs": pk["hbm_gbs"], "rotation": "distinct weight copies of 300 MB per shape (> L2) in one CUDA graph",
+    out["phi3_decode_sweep"] = {"peak_gbs": pk["hbm_gbs"], "weight_layout": "decode-stream layout (2 bits per trit); gbs and frac count its bytes",
+                                "rotation": "distinct weight copies of 300 MB per shape (> L2) in one CUDA graph",
                                 "cases": decode}
     out["phi3_prefill_2048"] = {"peak_tflops": pk["bf16_tflops"], "cases": prefill}
     return out
@@ -755,7 +785,7 @@ def quantize_pack_line(torch, dev, ops, pk):
     sec = e0.elapsed_time(e1) * 1e-3 / (reps * len(ws))
     alg = 4096 * 4096 * 4 + 4096 * 86 * 16 + 4096 * 4
     return {"bound": "hbm", "achieved": alg / sec / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
-            "frac": alg / sec / 1e9 / pk["hbm_gbs"], "us_per_launch": sec * 1e6, "kernel": "quantize_pack_row_kernel"}
+            "frac": alg / sec / 1e9 / pk["hbm_gbs"], "us_per_launch": sec * 1e6, "kernel": "quantize_pack_ring_kernel"}
 
 
 def run_kernel_case(args):
@@ -778,8 +808,14 @@ def run_kernel_case(args):
         scale = torch.rand(rows, device=dev, generator=gen)
         x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
         y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
-        calls = [lambda m=m: ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=scale, C=y) for m in mats] * 2
-        alg, unit, peak, name = rows * kl * 16 + 4 * rows + 2 * tok * k + 2 * tok * rows, "GB/s", pk["hbm_gbs"], "gemv_trit_lut_kernel"
+        if args.decode_layout == "t2":
+            t2s = [ops.pack_t2(m, rows, k) for m in mats]
+            calls = [lambda m=m: ops.gemm_trit_t2([m], [rows], x, K=k, row_scales=[scale], outs=[y]) for m in t2s] * 2
+            wbytes = t2s[0].numel()
+        else:
+            calls = [lambda m=m: ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=scale, C=y) for m in mats] * 2
+            wbytes = rows * kl * 16
+        alg, unit, peak, name = wbytes + 4 * rows + 2 * tok * k + 2 * tok * rows, "GB/s", pk["hbm_gbs"], "gemv_trit_lut_kernel"
     elif args.kernel == "gemm":
         rows, k, tok = HIDDEN, HIDDEN, BATCH * PREFILL
         kl = (k + 47) // 48
@@ -793,7 +829,7 @@ def run_kernel_case(args):
         ws = [torch.randn(4096, 4096, device=dev, generator=gen) * 0.02 for _ in range(8)]
         outs = [ops.quantize_pack(w, THRESHOLD, "absmean") for w in ws]
         calls = [lambda w=w, o=o: ops.quantize_pack(w, THRESHOLD, "absmean", out=o[0], row_scale_out=o[1]) for w, o in zip(ws, outs)] * 2
-        alg, unit, peak, name = 4096 * 4096 * 4 + 4096 * 86 * 16 + 4096 * 4, "GB/s", pk["hbm_gbs"], "quantize_pack_row_kernel"
+        alg, unit, peak, name = 4096 * 4096 * 4 + 4096 * 86 * 16 + 4096 * 4, "GB/s", pk["hbm_gbs"], "quantize_pack_ring_kernel"
     calls[0]()
     torch.cuda.synchronize()
     graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=dev)
@@ -837,6 +873,7 @@ def run_sweep(args):
         ws = [torch.randn(rows, k, device=dev, generator=gen) * 0.02 for _ in range(2)]
         mats = [ops.quantize_pack(ws[i % 2], THRESHOLD, "absmean") for i in range(copies)]
         bias = torch.randn(rows, device=dev, generator=gen) * 0.01
+        t2s = None
         for tok in (1, 4, 16, 2048):
             x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
             y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
@@ -874,6 +911,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", choices=["gemv", "gemm", "quantize", "sweep"], default=None,
                     help="time one kernel alone on a small case instead of the whole job (used for ncu captures)")
+    ap.add_argument("--decode-layout", choices=["t2", "limb"], default="t2",
+                    help="weight layout of the decode-sized calls: the decode-stream layout made once per weight (default) "
+                         "or the reference's packed limbs")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)

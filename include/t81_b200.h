@@ -288,6 +288,30 @@ T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, 
                                           int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
                                           float alpha, float beta, void *stream);
 
+/* The decode-stream layout ("T2") of a packed weight matrix, and TRIT mode on it.
+ *
+ * The limb layout is what the reference stores and what every other entry point takes; it costs 16 bytes per
+ * 48 trits and a base-27 decode per byte.  A weight that is multiplied again and again by a few activation rows
+ * (decoding) can be re-arranged ONCE into two bits per trit, ordered the way the tensor-core fragments of the
+ * streaming kernel want them: 12 bytes per 48 trits cross HBM and a trit decodes with a shift and a mask.
+ * The trits are identical; nothing about the arithmetic changes.  Layout: blocks of 32 rows x 192 columns, block
+ * (chunk c, row tile T) at byte (c * ceil(rows / 32) + T) * 1536; inside, lane l = 4 g + t owns the twelve 32-bit
+ * words at l * 48; word 6 gr + m / 2 (gr = 0, 1; m = 0..11) holds registers j = 4 (m % 2) + r, r = 0..3: the
+ * first trit's code in bits 15 - 2j, 14 - 2j, the second's in bits 31 - 2j, 30 - 2j, with
+ *   register r, trit h  <->  row 32 T + 16 gr + g + 8 (r % 2), column 192 c + 48 t + 4 m + 2 (r / 2) + h,
+ * code 01 = +1, 11 = -1, 00 = 0, rows and columns past the matrix 0.
+ *   t2_bytes:     size of the layout for a rows x cols matrix (a multiple of 1536), -1 on bad arguments.
+ *   pack_t2:      packed limbs (rows, ceil(cols/48), 16) -> T2 (16-byte aligned), on the device.
+ *   gemm_trit_t2: t81b200_gemm_trit_grouped with the matrices given in T2, for 1..16 rows of B (T81B200_ELIMIT
+ *                 beyond: prefill-sized products take the limb layout).  One launch.
+ * No counterpart in the reference (its packed copy per module, t81/nn/linear.py:84-99, is the limb layout). */
+T81B200_API int64_t t81b200_t2_bytes(int64_t rows, int64_t cols);
+T81B200_API int t81b200_pack_t2(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *t2, void *stream);
+T81B200_API int t81b200_gemm_trit_t2(int n_group, const uint8_t *const *t2, const float *const *row_scale,
+                                     const float *const *bias, void *const *C, const int64_t *M, const void *B,
+                                     int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
+                                     float alpha, float beta, void *stream);
+
 /* Quantisation-aware-training forward of t81.nn.Linear (t81/nn/linear.py:72-99, t81/qat.py:12-57), the parts
  * that touch every weight.
  *   qat_update_scale: candidate = max(max |w|, 1e-6); the first call stores it, later calls store

@@ -204,6 +204,36 @@ def addcmul(input, tensor1, tensor2, value: float = 1.0) -> np.ndarray:
 # when the block has no non-zero trit (the absmax the reference takes of trit * scale).
 
 
+def pack_t2(trits) -> np.ndarray:
+    """The decode-stream layout of a (rows, cols) trit matrix, as bytes (own format, no reference counterpart;
+    the statement in include/t81_b200.h restated): blocks of 32 rows x 192 columns, block (chunk c, row tile T)
+    at byte (c * tiles32 + T) * 1536; lane l = 4 g + t owns 12 little-endian 32-bit words at l * 48; word
+    6 gr + m // 2 holds registers j = 4 (m % 2) + r: trit h of register r <-> row 32 T + 16 gr + g + 8 (r % 2),
+    column 192 c + 48 t + 4 m + 2 (r // 2) + h, its code (01 = +1, 11 = -1, 00 = 0) at bits 15 - 2j, 14 - 2j
+    (h = 0) or 31 - 2j, 30 - 2j (h = 1)."""
+    trits = np.asarray(trits, dtype=np.int8)
+    rows, cols = trits.shape
+    tiles32, chunks = (rows + 31) // 32, (cols + 191) // 192
+    padded = np.zeros((tiles32 * 32, chunks * 192), np.int8)
+    padded[:rows, :cols] = trits
+    code = np.where(padded == 1, 1, np.where(padded == -1, 3, 0)).astype(np.uint32)
+    out = np.zeros((chunks, tiles32, 32, 12), np.uint32)
+    T = np.arange(tiles32)[None, :, None]
+    c = np.arange(chunks)[:, None, None]
+    lane = np.arange(32)[None, None, :]
+    g, t = lane >> 2, lane & 3
+    for gr in range(2):
+        for m in range(12):
+            for r in range(4):
+                j = 4 * (m % 2) + r
+                row = 32 * T + 16 * gr + g + 8 * (r % 2)
+                for h in range(2):
+                    col = 192 * c + 48 * t + 4 * m + 2 * (r // 2) + h
+                    shift = (30 if h else 14) - 2 * j
+                    out[:, :, :, 6 * gr + m // 2] |= code[row, col] << np.uint32(shift)
+    return out.astype("<u4").view(np.uint8).reshape(-1)
+
+
 def tq_encode(trits, row_scale, fmt: str) -> np.ndarray:
     t = np.ascontiguousarray(trits, dtype=np.int8)
     rows, cols = t.shape

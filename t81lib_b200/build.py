@@ -18,7 +18,7 @@ _CSRC = os.path.join(_PKG, "csrc")
 _LIBDIR = os.path.join(_PKG, "lib")
 LIB_PATH = os.path.join(_LIBDIR, "libt81_b200.so")
 
-SOURCES = ["capi.cu", "quantize_pack.cu", "gemm_limb.cu", "gemv_trit.cu", "gemv_trit_lut.cu", "gemm_trit_simt.cu", "gemm_trit_tc.cu", "elementwise.cu", "tq_codec.cu", "qat.cu"]
+SOURCES = ["capi.cu", "quantize_pack.cu", "gemm_limb.cu", "gemv_trit.cu", "gemv_trit_lut.cu", "gemm_trit_simt.cu", "gemm_trit_tc.cu", "elementwise.cu", "tq_codec.cu", "qat.cu", "pack_t2.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--fmad=true", "-prec-div=true", "-prec-sqrt=true",

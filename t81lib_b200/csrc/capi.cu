@@ -84,7 +84,7 @@ int gemm_trit_tc_status(int reset);
 int gemv_trit_status(int reset);
 int gemv_trit_lut_status(int reset);
 int quantize_pack_status(int reset);
-int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
+int gemv_trit_lut_launch(int fmt, int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
                          void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
                          int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx);
 
@@ -239,6 +239,31 @@ static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void 
     return gemm_trit_simt_launch(A, row_scale, B, b_dtype, layout, ldb, bias, C, c_dtype, ldc, M, N, K, alpha, beta, st);
 }
 
+extern "C" int t81b200_gemm_trit_t2(int n_group, const uint8_t *const *t2, const float *const *row_scale,
+                                    const float *const *bias, void *const *C, const int64_t *M, const void *B, int b_dtype,
+                                    int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K, float alpha, float beta,
+                                    void *stream) {
+    if (n_group < 1 || n_group > T81B200_MAX_GROUP)
+        return fail(T81B200_ELIMIT, "gemm_trit_t2: %d matrices, between 1 and %d are supported", n_group, T81B200_MAX_GROUP);
+    if (!t2 || !C || !M) return fail(T81B200_EINVAL, "gemm_trit_t2: null pointer");
+    if (N < 0 || K < 0) return fail(T81B200_EINVAL, "gemm_ternary dimensions must be non-negative");
+    if (N > 16) return fail(T81B200_ELIMIT, "gemm_trit_t2: %lld rows of B; the decode-stream layout serves 1 to 16", (long long)N);
+    if (!valid_dtype(b_dtype) || !valid_dtype(c_dtype)) return fail(T81B200_EINVAL, "gemm_trit: unknown dtype");
+    if (ldb < K) return fail(T81B200_EINVAL, "gemm_trit: ldb (%lld) below the row length (%lld)", (long long)ldb, (long long)K);
+    for (int i = 0; i < n_group; ++i) {
+        if (M[i] <= 0 || K <= 0) return fail(T81B200_EINVAL, "gemm_trit_t2: dimensions must be positive");
+        if (ldc < M[i]) return fail(T81B200_EINVAL, "gemm_trit: ldc (%lld) below the row length (%lld)", (long long)ldc, (long long)M[i]);
+        if (N > 0 && (!C[i] || !t2[i] || !B)) return fail(T81B200_EINVAL, "gemm_trit: null pointer");
+        if (reinterpret_cast<uintptr_t>(t2[i]) % 16 != 0) return fail(T81B200_EALIGN, "gemm_trit_t2: matrices must be 16-byte aligned");
+    }
+    if (int rc = check_device()) return rc;
+    if (N == 0) return T81B200_OK;
+    const int rc = gemv_trit_lut_launch(1, n_group, t2, row_scale, bias, C, M, B, b_dtype, ldb, c_dtype, ldc, (int)N, K, alpha, beta,
+                                        static_cast<cudaStream_t>(stream), nullptr);
+    if (rc == T81B200_EALIGN) return fail(T81B200_ELIMIT, "gemm_trit_t2: K = %lld does not fit the kernel's shared memory", (long long)K);
+    return rc;
+}
+
 extern "C" int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, const float *const *row_scale,
                                          const float *const *bias, void *const *C, const int64_t *M, const void *B,
                                          int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,
@@ -260,7 +285,7 @@ extern "C" int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, c
     if (N == 0) return T81B200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (streaming) {
-        const int rc = gemv_trit_lut_launch(n_group, A, row_scale, bias, C, M, B, b_dtype, ldb, c_dtype, ldc, (int)N, K, alpha,
+        const int rc = gemv_trit_lut_launch(0, n_group, A, row_scale, bias, C, M, B, b_dtype, ldb, c_dtype, ldc, (int)N, K, alpha,
                                             beta, st, nullptr);
         if (rc != T81B200_EALIGN) return rc;
     }

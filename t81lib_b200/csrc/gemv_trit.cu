@@ -753,7 +753,7 @@ int gemv_trit_status(int reset) {
 namespace {
 }  // namespace
 
-int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
+int gemv_trit_lut_launch(int fmt, int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
                          void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
                          int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx);
 
@@ -780,7 +780,7 @@ int gemv_trit_launch(const uint8_t *A, const float *row_scale, const void *X, in
     if (path == '\0') {
         const float *rs = row_scale, *bs = bias;
         void *cc = C;
-        const int rc = gemv_trit_lut_launch(1, &A, &rs, &bs, &cc, &M, X, x_dtype, ldx, c_dtype, ldc, ntok, K, alpha, beta, st, ctx);
+        const int rc = gemv_trit_lut_launch(0, 1, &A, &rs, &bs, &cc, &M, X, x_dtype, ldx, c_dtype, ldc, ntok, K, alpha, beta, st, ctx);
         if (rc != T81B200_EALIGN) {
             if (ctx && ctx->sync_local && rc == T81B200_OK) ctx->sync_fused = true;
             return rc;

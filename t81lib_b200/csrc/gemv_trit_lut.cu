@@ -28,6 +28,19 @@
 // rejects them, include/t81/core/limb.hpp:160-169).  Every weight word is masked to five bits per byte before
 // it is used as a table index and the table has 32 entries per position, the last five all zero: bytes 27..31
 // decode as the zero tryte and larger ones as some valid tryte; no look-up can leave the table.
+//
+// Second weight format, FMT == 1 ("T2", the decode-stream layout made once per weight matrix by t81b200_pack_t2):
+// two bits per trit, already in the order the mma.sync A fragments want them.  The matrix is cut into blocks of
+// 32 rows x 192 columns (one warp's rows, one chunk); block (chunk c, row tile T) lies at byte
+// (c * tiles32 + T) * 1536 and holds, for lane l = 4 g + t, twelve 32-bit words at l * 48: word 6 gr + m / 2 serves
+// the 16-row group gr and the multiply m = 0..11 of the chunk; register r = 0..3 of that multiply sits at
+// j = 4 (m % 2) + r: its low-half code in bits 15-2j, 14-2j and its high-half code in bits 31-2j, 30-2j, where
+//   register r, half h  <->  row 32 T + 16 gr + g + 8 (r % 2),  column 192 c + 48 t + 4 m + 2 (r / 2) + h,
+// and a code is 01 for +1, 11 for -1, 00 for 0: shifted to the top of a 16-bit half it IS the bf16 number
+// +2, -2 or 0.  Decoding a register is one shift and one AND — no table, no shared-memory traffic beyond the
+// 48 bytes per lane and chunk — and the factor 2 is taken out with alpha.  A stage of the ring (all RW row
+// tiles of a chunk) is contiguous in memory: one bulk copy, no tensor map.  A quarter fewer bytes than the
+// limb layout cross HBM.
 #include "common.cuh"
 #include "tma.cuh"
 #include "exchange.cuh"
@@ -93,6 +106,8 @@ struct LutSeg {
     void *C;                 // (ntok, M) row-major, ldc elements
     int64_t M;
     int tile_begin;          // first row tile (blockIdx.x) of this segment
+    const uint8_t *t2;       // FMT 1: the matrix in the decode-stream layout
+    int tiles32;             // FMT 1: 32-row tiles of the matrix
 };
 
 struct GemvLutParams {
@@ -115,6 +130,8 @@ struct GemvLutParams {
     uint32_t *sync_local;
     uint32_t *sync_peer[T81B200_MAX_PEERS];
     int trace_slot;          // instrumented builds: which trace record this launch writes
+    uint32_t shl[8];         // FMT 1: 4^j.  Multiplying by a launch-time constant instead of shifting by a literal puts
+                             // the shifts of the decode on the multiply-add pipe, beside the masks on the logic pipe
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -211,7 +228,7 @@ __device__ __forceinline__ void stage_elements(const GemvLutParams &p, int L0, i
     }
 }
 
-template <typename XT, typename CT, int TOKB>
+template <typename XT, typename CT, int TOKB, int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                      const __grid_constant__ CUtensorMap map2, const GemvLutParams p) {
@@ -226,7 +243,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     // The table window was laid out for dynamic shared memory starting below kMaxBase.  Should it start higher,
     // the CTA still walks through every barrier (its cluster peers read its shared memory) but streams nothing,
     // and the launch reports LUT_STATUS_LAYOUT.
-    const bool layout_ok = base_off < kMaxBase;
+    const bool layout_ok = FMT == 1 || base_off < kMaxBase;  // the T2 format uses no table
     if (!layout_ok && threadIdx.x == 0) atomicCAS(&g_lut_status, LUT_STATUS_OK, LUT_STATUS_LAYOUT);
     uint8_t *lut = smem + (layout_ok ? kLutAbs - base_off : (uint32_t)kWindowLo);
     const int consumer_warps = p.row_warps * p.k_warps;
@@ -333,19 +350,29 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
                 const int st = c % p.stages;
                 const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
                 if (!mbar_wait(empty_bar(st), phase ^ 1u)) return false;
-                mbar_arrive_expect_tx(full_bar(st), (uint32_t)p.stage_bytes);
-                tma_load_2d(base + (uint32_t)ring_offset(st), map_w, (L0 + 4 * c) * 16, (int)cta_row0, full_bar(st));
+                if constexpr (FMT == 1) {
+                    // the chunk's blocks of this CTA's row tiles are contiguous; the matrix's last tiles may be fewer
+                    const int tile0 = ((int)blockIdx.x - S.tile_begin) * p.row_warps;
+                    const int ntile = S.tiles32 - tile0 < p.row_warps ? S.tiles32 - tile0 : p.row_warps;
+                    mbar_arrive_expect_tx(full_bar(st), (uint32_t)ntile * 1536u);
+                    bulk_load(base + (uint32_t)ring_offset(st), S.t2 + ((int64_t)(L0 / 4 + c) * S.tiles32 + tile0) * 1536,
+                              (uint32_t)ntile * 1536u, full_bar(st));
+                } else {
+                    mbar_arrive_expect_tx(full_bar(st), (uint32_t)p.stage_bytes);
+                    tma_load_2d(base + (uint32_t)ring_offset(st), map_w, (L0 + 4 * c) * 16, (int)cta_row0, full_bar(st));
+                }
                 return true;
             };
             // decode tables (a compile-time image in global memory), row scales and biases: bulk copies, none of
             // them the previous kernel's output.  Scales and biases that a copy cannot take (unaligned, or a tile
             // that reaches past the last row) are fetched by the consumer threads instead.
             if (layout_ok) {
-                uint32_t bytes = (uint32_t)kLutBytes;
+                uint32_t bytes = FMT == 1 ? 0u : (uint32_t)kLutBytes;
                 if (scale_by_copy) bytes += (uint32_t)rows_per_cta * 4u;
                 if (bias_by_copy) bytes += (uint32_t)rows_per_cta * 4u;
-                mbar_arrive_expect_tx(pro_bar, bytes);
-                bulk_load(smem_u32(lut), &g_lut_image, (uint32_t)kLutBytes, pro_bar);
+                if (bytes) mbar_arrive_expect_tx(pro_bar, bytes);
+                else mbar_arrive(pro_bar);
+                if constexpr (FMT == 0) bulk_load(smem_u32(lut), &g_lut_image, (uint32_t)kLutBytes, pro_bar);
                 if (scale_by_copy) bulk_load(smem_u32(sb), S.row_scale + cta_row0, (uint32_t)rows_per_cta * 4u, pro_bar);
                 if (bias_by_copy) bulk_load(smem_u32(sb + rows_per_cta), S.bias + cta_row0, (uint32_t)rows_per_cta * 4u, pro_bar);
             }
@@ -406,11 +433,53 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         const uint32_t lane_off = (uint32_t)((rw * 32 + g) * 64 + t * 16);
         const uint32_t lane_key = window | kLutAbs | (uint32_t)((lane & 15) << 3);
         if (layout_ok) ok = __all_sync(0xffffffffu, mbar_wait(pro_bar, 0));
-        for (int c = kw; c < chunks_cta && ok; c += p.k_warps) {
-            const int st = c % p.stages;
-            const uint32_t phase = (uint32_t)(c / p.stages) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(st), phase) && (!p.bulk_x || mbar_wait(x_bar + 8u * (c / x_group), 0)));
+        // ring slot, its phase and the activation piece of chunk c, carried along instead of divided out
+        // (the ring has at least k_warps slots)
+        int st = kw % p.stages, xg = 0, xc = kw;
+        uint32_t phase = (uint32_t)(kw / p.stages) & 1u;
+        for (int c = kw; c < chunks_cta && ok; c += p.k_warps, st += p.k_warps, xc += p.k_warps) {
+            if (st >= p.stages) { st -= p.stages; phase ^= 1u; }
+            while (xc >= x_group) { xc -= x_group; ++xg; }
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(st), phase) && (!p.bulk_x || mbar_wait(x_bar + 8u * xg, 0)));
             if (!ok) break;
+            if constexpr (FMT == 1) {
+                const uint8_t *tile = smem + ring_offset(st) + rw * 1536 + lane * 48;
+                uint32_t wd[12];
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    const uint4 q = *reinterpret_cast<const uint4 *>(tile + 16 * j);
+                    wd[4 * j] = q.x; wd[4 * j + 1] = q.y; wd[4 * j + 2] = q.z; wd[4 * j + 3] = q.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(st));  // the codes are in registers: the slot can be refilled
+                uint4 xr[TOKB][PLANES][6];
+#pragma unroll
+                for (int b = 0; b < TOKB; ++b)
+#pragma unroll
+                    for (int pl = 0; pl < PLANES; ++pl) {
+                        const uint4 *xv = reinterpret_cast<const uint4 *>(xs + pl * plane_stride + tok_off[b] + c * 96);
+#pragma unroll
+                        for (int q = 0; q < 6; ++q) xr[b][pl][q] = xv[q];
+                    }
+#pragma unroll
+                for (int m = 0; m < 12; ++m) {
+#pragma unroll
+                    for (int gr = 0; gr < 2; ++gr) {
+                        const uint32_t w = wd[6 * gr + (m >> 1)];
+                        const int j0 = 4 * (m & 1);
+                        const uint32_t a0 = (j0 ? w * p.shl[j0] : w) & 0xC000C000u, a1 = (w * p.shl[j0 + 1]) & 0xC000C000u;
+                        const uint32_t a2 = (w * p.shl[j0 + 2]) & 0xC000C000u, a3 = (w * p.shl[j0 + 3]) & 0xC000C000u;
+#pragma unroll
+                        for (int b = 0; b < TOKB; ++b)
+#pragma unroll
+                            for (int pl = 0; pl < PLANES; ++pl) {
+                                const uint32_t *xw = reinterpret_cast<const uint32_t *>(&xr[b][pl][0]) + 2 * m;
+                                mma_bf16_16816(acc[gr][m % NACC][b], a0, a1, a2, a3, xw[0], xw[1]);
+                            }
+                    }
+                }
+                continue;
+            }
             const uint8_t *tile = smem + ring_offset(st) + lane_off;
             uint4 limb[4];
 #pragma unroll
@@ -488,7 +557,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         if (tok >= p.ntok) return;
         float y[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = v[i] * p.alpha * sb[r0 + i] + sb[rows_per_cta + r0 + i];
+        for (int i = 0; i < 8; ++i) y[i] = v[i] * p.alpha * sb[r0 + i] + sb[rows_per_cta + r0 + i];  // FMT 1: alpha arrives halved
         const int64_t row = cta_row0 + r0;
         CT *c = static_cast<CT *>(S.C) + (int64_t)tok * p.ldc + row;
         if (vec_store && row + 8 <= S.M) {
@@ -530,7 +599,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         // finishes those rows (slot = the sender's rank), one cluster barrier orders the writes before the reads,
         // and the finisher adds the slots in rank order.  After the barrier no CTA touches another's memory, so
         // none has to outlive the others.
-        const int span = rows_per_cta / slices;  // a multiple of 8: 32*RW rows, 2 or 4 slices
+        const int span = rows_per_cta / slices;  // a multiple of 8: 32*RW rows; 2, 4 or (RW even) 8 slices
         const int spitch = span + 4;
         const int slot = kTokPad * spitch;       // floats per sender
         float *recv = part + (size_t)p.k_warps * plane;
@@ -602,7 +671,7 @@ struct PlanKey {
     const void *A[kMaxSeg];
     int64_t M[kMaxSeg];
     int64_t K;
-    int n_seg, ntok, x_dtype, c_dtype, device;
+    int n_seg, ntok, x_dtype, c_dtype, device, fmt;
     bool operator==(const PlanKey &o) const { return memcmp(this, &o, sizeof *this) == 0; }
 };
 struct PlanKeyHash {
@@ -628,9 +697,9 @@ std::unordered_map<PlanKey, Plan, PlanKeyHash> g_plans;
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared-memory layout for a launch shape; false when it does not fit.
-bool lay_out(Plan &pl, int planes, int ntok, int tokpad, int rwv, int kwv, int s, int lps, int chunks) {
+bool lay_out(Plan &pl, int fmt, int planes, int ntok, int tokpad, int rwv, int kwv, int s, int lps, int chunks) {
     const int rows = 32 * rwv;
-    const size_t stage_bytes = (size_t)rows * 64;
+    const size_t stage_bytes = (size_t)rows * (fmt == 1 ? 48 : 64);
     const size_t xs_bytes = align_up((size_t)planes * ntok * (lps * 24 + 4) * 4, 128);
     // partial sums of the K-slices, and behind them the receive slots of the cluster fold (one per rank)
     const size_t part_bytes = align_up((size_t)kwv * tokpad * (rows + 4) * 4 + (s > 1 ? (size_t)tokpad * (rows + 4 * s) * 4 : 0), 128);
@@ -669,16 +738,17 @@ int make_plan(Plan &pl, const PlanKey &key) {
     Plan best;
     for (int rwv = 1; rwv <= 8; ++rwv)
         for (int kwv = 1; rwv * kwv <= kMaxConsumerWarps; ++kwv)
-            for (int s = 1; s <= 4; s *= 2) {
+            for (int s = 1; s <= 8; s *= 2) {
+                if (s == 8 && rwv % 2) continue;  // the fold hands every rank a multiple of 8 rows
                 if (sw.rw && (rwv != sw.rw || kwv != sw.kw || s != (sw.s ? sw.s : 1))) continue;
-                if (!sw.rw && kwv != 2 && kwv != 4 && kwv != 8) continue;
                 int lps = (kl4 / 4 + s - 1) / s * 4;
                 if (lps < 4) lps = 4;
+                if (!sw.rw && kwv != 2 && kwv != 4 && kwv != 8 && !(kwv == 1 && lps == 4)) continue;  // one warp for a single chunk
                 if (s > 1 && (int64_t)(s - 1) * lps >= kl4) continue;  // an empty slice
                 const int chunks = lps / 4;
                 if (kwv > chunks) continue;                            // a warp without work
                 Plan cand;
-                if (!lay_out(cand, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks)) continue;
+                if (!lay_out(cand, key.fmt, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks)) continue;
                 const int rows = 32 * rwv;
                 int64_t row_tiles = 0;
                 for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;
@@ -688,15 +758,23 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 // L2, which delivers about 5 TB/s when all CTAs ask for the same lines at once; the longer of the
                 // two bounds the CTA and a fifth of the shorter is not hidden; a launch costs 1.5 us, a cluster's
                 // fold 0.5 to 0.7 us more.  Clusters must fit inside a GPC: fewer CTAs are co-resident than SMs.
-                const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : sms - 20);
+                const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : (s == 4 ? sms - 20 : sms - 36));
                 const double waves = ceil((double)row_tiles * s / wave_ctas);
                 const double warps_per_sched = rwv * kwv / 4.0;
                 const double chunks_per_warp = 0.3 * ceil((double)chunks / kwv) + 0.7 * (double)chunks / kwv;
-                const double work = chunks_per_warp * 0.6e-6 * (1.0 + 0.4 * (planes * (tokpad / 8) - 1)) *
-                                    (warps_per_sched > 3.0 ? warps_per_sched / 3.0 : 1.0);
-                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / 5.0e12;
-                const double t = waves * (1.5e-6 + (s == 2 ? 0.7e-6 : (s == 4 ? 0.5e-6 : 0.0)) +
-                                          (work > x_fetch ? work + 0.2 * x_fetch : x_fetch + 0.2 * work));
+                // The decode-stream layout has its own fit (mean regret 4 % over the same sweep): a chunk costs a
+                // warp half as much (no table look-ups), two warps per scheduler already saturate it, the
+                // activations arrive faster relative to the work, half of the shorter bound is not hidden, and
+                // the cluster fold is cheap.
+                const bool t2 = key.fmt == 1;
+                const double per_chunk = t2 ? 0.3e-6 : 0.6e-6, sched_cap = t2 ? 2.0 : 3.0;
+                const double work = chunks_per_warp * per_chunk * (1.0 + 0.4 * (planes * (tokpad / 8) - 1)) *
+                                    (warps_per_sched > sched_cap ? warps_per_sched / sched_cap : 1.0);
+                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / (t2 ? 8.0e12 : 5.0e12);
+                const double fold = t2 ? (s == 2 ? 0.3e-6 : (s == 8 ? 0.3e-6 : 0.0))
+                                       : (s == 2 ? 0.7e-6 : (s == 4 ? 0.5e-6 : (s == 8 ? 0.8e-6 : 0.0)));
+                const double hidden = t2 ? 0.5 : 0.2;
+                const double t = waves * (1.5e-6 + fold + (work > x_fetch ? work + hidden * x_fetch : x_fetch + hidden * work));
                 if (t < best_t) {
                     best_t = t;
                     best = cand;
@@ -710,19 +788,21 @@ int make_plan(Plan &pl, const PlanKey &key) {
     for (int i = 0; i < key.n_seg; ++i) {
         best.tile_begin[i] = tile;
         tile += (int)((key.M[i] + rows - 1) / rows);
+        if (key.fmt == 1) continue;  // contiguous stages: bulk copies, no tensor map
         if (int rc = make_map_2d(&best.map[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, key.A[i], (uint64_t)kl * 16, (uint64_t)key.M[i],
                                  (uint64_t)kl * 16, 64, (uint32_t)rows, CU_TENSOR_MAP_SWIZZLE_NONE))
             return rc;
     }
+    if (key.fmt == 1) memset(best.map, 0, sizeof best.map);
     for (int i = key.n_seg; i < kMaxSeg; ++i) { best.tile_begin[i] = tile; best.map[i] = best.map[0]; }
     best.valid = true;
     pl = best;
     return T81B200_OK;
 }
 
-template <typename XT, typename CT, int TOKB>
+template <typename XT, typename CT, int TOKB, int FMT>
 int launch_lut(const Plan &pl, const GemvLutParams &p, cudaStream_t st) {
-    auto kern = gemv_trit_lut_kernel<XT, CT, TOKB>;
+    auto kern = gemv_trit_lut_kernel<XT, CT, TOKB, FMT>;
     // the shared-memory limit is a per-device attribute of the function: raised once per device
     static std::atomic<bool> configured[64];
     int dev = 0;
@@ -749,30 +829,41 @@ int launch_lut(const Plan &pl, const GemvLutParams &p, cudaStream_t st) {
     return T81B200_OK;
 }
 
-template <typename XT>
+template <typename XT, int FMT>
 int launch_lut_ct(const Plan &pl, const GemvLutParams &p, int c_dtype, cudaStream_t st) {
     const bool wide = p.ntok > 8;
     switch (c_dtype) {
-        case T81B200_F32: return wide ? launch_lut<XT, float, 2>(pl, p, st) : launch_lut<XT, float, 1>(pl, p, st);
-        case T81B200_BF16: return wide ? launch_lut<XT, __nv_bfloat16, 2>(pl, p, st) : launch_lut<XT, __nv_bfloat16, 1>(pl, p, st);
-        case T81B200_F16: return wide ? launch_lut<XT, __half, 2>(pl, p, st) : launch_lut<XT, __half, 1>(pl, p, st);
+        case T81B200_F32: return wide ? launch_lut<XT, float, 2, FMT>(pl, p, st) : launch_lut<XT, float, 1, FMT>(pl, p, st);
+        case T81B200_BF16: return wide ? launch_lut<XT, __nv_bfloat16, 2, FMT>(pl, p, st) : launch_lut<XT, __nv_bfloat16, 1, FMT>(pl, p, st);
+        case T81B200_F16: return wide ? launch_lut<XT, __half, 2, FMT>(pl, p, st) : launch_lut<XT, __half, 1, FMT>(pl, p, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
+}
+
+template <int FMT>
+int launch_lut_xt(const Plan &pl, const GemvLutParams &p, int x_dtype, int c_dtype, cudaStream_t st) {
+    switch (x_dtype) {
+        case T81B200_BF16: return launch_lut_ct<__nv_bfloat16, FMT>(pl, p, c_dtype, st);
+        case T81B200_F32: return launch_lut_ct<float, FMT>(pl, p, c_dtype, st);
+        case T81B200_F16: return launch_lut_ct<__half, FMT>(pl, p, c_dtype, st);
+    }
+    return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
 }
 
 }  // namespace
 
 extern thread_local int g_hint_independent;
 
-// Launch of the table-decode streaming kernel over n_seg weight matrices that share X.  NK layout, ntok in 1..16,
-// every A 16-byte aligned.  Returns T81B200_EALIGN when no launch shape fits (K too long for shared memory).
-int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
+// Launch of the streaming kernel over n_seg weight matrices that share X.  NK layout, ntok in 1..16, every A
+// 16-byte aligned; fmt 0: A in the packed-limb layout (table decode), fmt 1: A in the decode-stream layout.
+// Returns T81B200_EALIGN when no launch shape fits (K too long for shared memory).
+int gemv_trit_lut_launch(int fmt, int n_seg, const uint8_t *const *A, const float *const *row_scale, const float *const *bias,
                          void *const *C, const int64_t *M, const void *X, int x_dtype, int64_t ldx, int c_dtype,
                          int64_t ldc, int ntok, int64_t K, float alpha, float beta, cudaStream_t st, const PeerCtx *ctx) {
     PlanKey key;
     memset(&key, 0, sizeof key);
     for (int i = 0; i < n_seg; ++i) { key.A[i] = A[i]; key.M[i] = M[i]; }
-    key.K = K; key.n_seg = n_seg; key.ntok = ntok; key.x_dtype = x_dtype; key.c_dtype = c_dtype;
+    key.K = K; key.n_seg = n_seg; key.ntok = ntok; key.x_dtype = x_dtype; key.c_dtype = c_dtype; key.fmt = fmt;
     T81_CUDA_TRY(cudaGetDevice(&key.device));
     Plan pl;
     {
@@ -796,9 +887,11 @@ int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const 
         p.seg[i].C = C[j];
         p.seg[i].M = M[j];
         p.seg[i].tile_begin = pl.tile_begin[i];
+        p.seg[i].t2 = A[j];
+        p.seg[i].tiles32 = (int)((M[j] + 31) / 32);
     }
     p.n_seg = n_seg;
-    p.X = X; p.K = K; p.kl = (K + 47) / 48; p.ldx = ldx; p.ldc = ldc; p.ntok = ntok; p.alpha = alpha; p.beta = beta;
+    p.X = X; p.K = K; p.kl = (K + 47) / 48; p.ldx = ldx; p.ldc = ldc; p.ntok = ntok; p.alpha = fmt == 1 ? 0.5f * alpha : alpha; p.beta = beta;
     p.row_warps = pl.row_warps; p.k_warps = pl.k_warps; p.limbs_per_slice = pl.limbs_per_slice;
     p.stages = pl.stages; p.stage_bytes = pl.stage_bytes; p.ring0_stages = pl.ring0_stages; p.ring1_offset = pl.ring1_offset;
     p.xs_offset = pl.xs_offset; p.part_offset = pl.part_offset; p.sb_offset = pl.sb_offset; p.bar_offset = pl.bar_offset;
@@ -808,16 +901,12 @@ int gemv_trit_lut_launch(int n_seg, const uint8_t *const *A, const float *const 
     p.sync_local = ctx ? ctx->sync_local : nullptr;
     for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.sync_peer[i] = p.sync_local && i < ctx->n_peers ? ctx->sync_slots[i] : nullptr;
     p.independent = (g_hint_independent && !p.sync_local) ? 1 : 0;
+    for (int j = 0; j < 8; ++j) p.shl[j] = 1u << (2 * j);
 #ifdef T81B200_GEMV_TRACE
     static std::atomic<int> trace_counter{0};
     p.trace_slot = trace_counter.fetch_add(1);
 #endif
-    switch (x_dtype) {
-        case T81B200_BF16: return launch_lut_ct<__nv_bfloat16>(pl, p, c_dtype, st);
-        case T81B200_F32: return launch_lut_ct<float>(pl, p, c_dtype, st);
-        case T81B200_F16: return launch_lut_ct<__half>(pl, p, c_dtype, st);
-    }
-    return fail(T81B200_EINVAL, "gemm_trit: unknown activation dtype %d", x_dtype);
+    return fmt == 1 ? launch_lut_xt<1>(pl, p, x_dtype, c_dtype, st) : launch_lut_xt<0>(pl, p, x_dtype, c_dtype, st);
 }
 
 #ifdef T81B200_GEMV_TRACE

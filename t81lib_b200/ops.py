@@ -216,8 +216,29 @@ def gemm_trit(packed: torch.Tensor, B: torch.Tensor, *, M: int, K: int, layout: 
     return C
 
 
+def pack_t2(packed: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """Packed limbs -> the decode-stream layout (two bits per trit in tensor-core fragment order), uint8 of
+    ``t2_bytes(rows, cols)`` bytes on the same device.  Made once per weight; ``gemm_trit_t2`` multiplies it."""
+    _require_cuda(packed, "packed")
+    packed = packed.contiguous()
+    if packed.dtype != torch.uint8 or packed.numel() != rows * ((cols + 47) // 48) * 16:
+        raise ValueError("packed does not hold rows x ceil(cols/48) limbs")
+    out = torch.empty(int(_capi.lib.t81b200_t2_bytes(rows, cols)), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _capi.check(_capi.lib.t81b200_pack_t2(_ptr(packed), rows, cols, _ptr(out), _stream(packed.device)))
+    return out
+
+
+def gemm_trit_t2(t2, rows, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
+                 out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0):
+    """``gemm_trit_grouped`` on matrices in the decode-stream layout: ``t2`` is a list of ``pack_t2`` results,
+    ``rows`` their row counts, ``x`` (1..16 tokens, K).  One kernel launch."""
+    return gemm_trit_grouped(t2, x, K=K, row_scales=row_scales, biases=biases, outs=outs, out_dtype=out_dtype,
+                             alpha=alpha, beta=beta, _t2_rows=[int(r) for r in rows])
+
+
 def gemm_trit_grouped(packed, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
-                      out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0):
+                      out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0, _t2_rows=None):
     """TRIT mode for up to ``_capi.MAX_GROUP`` weight matrices that share their activations (q/k/v, gate/up):
     ``x`` is (tokens, K); returns the list of (tokens, rows_i) results.  With at most 16 tokens the whole
     group is one kernel launch.  ``outs`` may give the result tensors (same dtype, same leading stride)."""
@@ -230,9 +251,11 @@ def gemm_trit_grouped(packed, x: torch.Tensor, *, K: int, row_scales=None, biase
     if x.stride(1) != 1 and x.numel() > 0:
         x = x.contiguous()
     dev, tokens = x.device, x.shape[0]
-    rows = [int(p.shape[0]) for p in packed]
+    rows = _t2_rows if _t2_rows is not None else [int(p.shape[0]) for p in packed]
     for p in packed:
         _require_cuda(p, "packed")
+    if _t2_rows is not None and not 1 <= tokens <= 16:
+        raise ValueError("the decode-stream layout serves 1 to 16 tokens")
     if outs is None:
         if beta != 0.0:
             raise ValueError("beta != 0 needs outs")
@@ -260,7 +283,8 @@ def gemm_trit_grouped(packed, x: torch.Tensor, *, K: int, row_scales=None, biase
     arr = lambda ts: (vp * n)(*[None if t is None else t.data_ptr() for t in ts])  # noqa: E731
     ldb = x.stride(0) if tokens > 1 else max(K, 1)
     with torch.cuda.device(dev):
-        _capi.check(_capi.lib.t81b200_gemm_trit_grouped(
+        entry = _capi.lib.t81b200_gemm_trit_grouped if _t2_rows is None else _capi.lib.t81b200_gemm_trit_t2
+        _capi.check(entry(
             n, arr(packed), arr(scales), arr(bs), arr(outs), (ctypes.c_int64 * n)(*rows), _ptr(x), _dtype_code(x, "x"),
             ldb, _dtype_code(outs[0], "out"), ldc, tokens, K, float(alpha), float(beta), _stream(dev)))
     return outs
