@@ -190,6 +190,11 @@ T81B200_API int t81b200_gemm_limb_auto(const uint8_t *A, const uint8_t *B, float
 T81B200_API int t81b200_gemm_trit_auto(const uint8_t *A, const float *B, float *C, int64_t M, int64_t N,
                                        int64_t K, float alpha, float beta);
 
+/* Frees, on every device, the staging buffers that the _host and _auto entry points keep between calls (they grow
+ * to the largest operands seen and are otherwise held until the process ends).  No call may be in flight.  No
+ * counterpart in the reference (its CUDA path allocates and frees per call, src/linalg/gemm_cuda.cu:285-341). */
+T81B200_API int t81b200_release_staging(void);
+
 /* The four fp32 elementwise helpers of the reference's CUDA backend slot
  * (cuda_where / cuda_clamp / cuda_lerp / cuda_addcmul, include/t81/linalg/gemm_gpu.hpp:75-78,217-231;
  * kernels src/linalg/gemm_cuda.cu:165-283; CPU forms src/linalg/gemm_dispatch.cpp:147-222), over

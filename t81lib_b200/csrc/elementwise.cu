@@ -93,6 +93,21 @@ extern "C" int t81b200_elementwise(int op, const float *a, const float *b, const
     }
 }
 
+namespace t81b200 {
+void release_elementwise_staging() {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) return;
+    for (int d = 0; d < count && d < 64; ++d) {
+        EwStaging &stg = g_ew_staging[d];
+        std::lock_guard<std::mutex> lock(stg.mu);
+        bool any = false;
+        for (int i = 0; i < 4; ++i) any = any || stg.buf[i];
+        if (!any || cudaSetDevice(d) != cudaSuccess) continue;
+        for (int i = 0; i < 4; ++i) { if (stg.buf[i]) cudaFree(stg.buf[i]); stg.buf[i] = nullptr; stg.cap[i] = 0; }
+    }
+}
+}  // namespace t81b200
+
 extern "C" int t81b200_elementwise_auto(int op, const float *a, const float *b, const float *c, float *out, int64_t n,
                                         float s0, float s1) {
     if (n < 0) return fail(T81B200_EINVAL, "elementwise: negative length");

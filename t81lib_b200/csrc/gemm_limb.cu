@@ -99,6 +99,8 @@ int grow(void **p, size_t *cap, size_t need) {
 
 // 1: memory a kernel of the current device can dereference (device or managed memory);
 // 0: host memory (pageable or pinned).  Null pointers count as "either".
+void release_elementwise_staging();  // elementwise.cu
+
 int pointer_is_device(const void *p, int *is_device) {
     *is_device = 0;
     if (!p) return T81B200_OK;
@@ -115,6 +117,26 @@ int pointer_is_device(const void *p, int *is_device) {
 }  // namespace t81b200
 
 using namespace t81b200;
+
+extern "C" int t81b200_release_staging(void) {
+    if (int rc = check_device()) return rc;
+    int cur = 0, count = 0;
+    T81_CUDA_TRY(cudaGetDevice(&cur));
+    T81_CUDA_TRY(cudaGetDeviceCount(&count));
+    for (int d = 0; d < count && d < kMaxDevices; ++d) {
+        HostStaging &s = g_staging[d];
+        std::lock_guard<std::mutex> lock(s.mu);
+        if (!s.a && !s.b && !s.c && !s.ws) continue;
+        T81_CUDA_TRY(cudaSetDevice(d));
+        void **bufs[4] = {&s.a, &s.b, &s.c, &s.ws};
+        for (void **b : bufs) { if (*b) cudaFree(*b); *b = nullptr; }
+        s.a_cap = s.b_cap = s.c_cap = s.ws_cap = 0;
+    }
+    T81_CUDA_TRY(cudaSetDevice(cur));
+    release_elementwise_staging();
+    T81_CUDA_TRY(cudaSetDevice(cur));
+    return T81B200_OK;
+}
 
 extern "C" int t81b200_gemm_limb(const uint8_t *A, const uint8_t *B, float *C, int64_t M, int64_t N,
                                  int64_t k_limbs, float alpha, float beta, void *stream) {
