@@ -648,9 +648,12 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
 //                                                 that try many shapes in one process)
 struct Switches {
     int rw = 0, kw = 0, s = 0;
+    int smem_cap = 0, max_warps = 0;  // experiment: T81B200_GEMV_LIMITS="shared bytes,consumer warps"
     bool pdl = true, live = false;
     void read_cfg() {
         rw = kw = s = 0;
+        smem_cap = max_warps = 0;
+        if (const char *env = getenv("T81B200_GEMV_LIMITS")) sscanf(env, "%d,%d", &smem_cap, &max_warps);
         if (const char *env = getenv("T81B200_GEMV_CFG")) sscanf(env, "%d,%d,%d", &rw, &kw, &s);
     }
     Switches() {
@@ -697,7 +700,7 @@ std::unordered_map<PlanKey, Plan, PlanKeyHash> g_plans;
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared-memory layout for a launch shape; false when it does not fit.
-bool lay_out(Plan &pl, int fmt, int planes, int ntok, int tokpad, int rwv, int kwv, int s, int lps, int chunks) {
+bool lay_out(Plan &pl, int fmt, int planes, int ntok, int tokpad, int rwv, int kwv, int s, int lps, int chunks, int budget) {
     const int rows = 32 * rwv;
     const size_t stage_bytes = (size_t)rows * (fmt == 1 ? 48 : 64);
     const size_t xs_bytes = align_up((size_t)planes * ntok * (lps * 24 + 4) * 4, 128);
@@ -705,14 +708,14 @@ bool lay_out(Plan &pl, int fmt, int planes, int ntok, int tokpad, int rwv, int k
     const size_t part_bytes = align_up((size_t)kwv * tokpad * (rows + 4) * 4 + (s > 1 ? (size_t)tokpad * (rows + 4 * s) * 4 : 0), 128);
     const size_t sb_bytes = align_up((size_t)2 * rows * 4, 128);
     const size_t bar_bytes = 1024;  // 2 * 48 + 1 barriers
-    size_t off = kWindowHi;
+    size_t off = fmt == 1 ? 0 : kWindowHi;  // no table, no window to keep free
     pl.xs_offset = (int)off; off += xs_bytes;
     pl.part_offset = (int)off; off += part_bytes;
     pl.sb_offset = (int)off; off += sb_bytes;
     pl.bar_offset = (int)off; off += bar_bytes;
-    if (off > (size_t)kSmemBudget) return false;
-    int stages0 = (int)(kWindowLo / stage_bytes);
-    int stages1 = (int)(((size_t)kSmemBudget - off) / stage_bytes);
+    if (off > (size_t)budget) return false;
+    int stages0 = fmt == 1 ? 0 : (int)(kWindowLo / stage_bytes);
+    int stages1 = (int)(((size_t)budget - off) / stage_bytes);
     int stages = stages0 + stages1;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages > chunks) stages = chunks;
@@ -748,7 +751,8 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 const int chunks = lps / 4;
                 if (kwv > chunks) continue;                            // a warp without work
                 Plan cand;
-                if (!lay_out(cand, key.fmt, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks)) continue;
+                if (sw.max_warps && rwv * kwv > sw.max_warps) continue;
+                if (!lay_out(cand, key.fmt, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks, sw.smem_cap ? sw.smem_cap : kSmemBudget)) continue;
                 const int rows = 32 * rwv;
                 int64_t row_tiles = 0;
                 for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;

@@ -21,6 +21,9 @@ def main() -> int:
     from t81lib_b200 import torch as t81_torch
     from t81lib_b200.nn.sharded import ShardedLinear
 
+    # every product below, sharded or whole, runs on the packed limbs: the comparison is bit for bit, and the
+    # decode-stream layout (used for <= 16 tokens otherwise) accumulates in another order than the peer-store kernel
+    t81_torch.DECODE_STREAM_LAYOUT = False
     gen = torch.Generator(device=dev).manual_seed(5)  # same values on every rank
     w = torch.randn(1024, 520, generator=gen, device=dev) * 0.02
     b = torch.randn(1024, generator=gen, device=dev) * 0.01
