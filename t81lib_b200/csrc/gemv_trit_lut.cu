@@ -420,7 +420,7 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         }
         bool ok = true;
         if (p.bulk_x) {
-            if (lane == 0) issue_x(warp, consumer_warps);
+            issue_x(warp + lane * consumer_warps, 32 * consumer_warps);  // one copy per lane at most: one instruction per warp
         } else {
             stage_elements<XT, PLANES>(p, L0, nl, xs, tok_stride, plane_stride, threadIdx.x, consumer_threads);
             asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory");
@@ -648,12 +648,9 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
 //                                                 that try many shapes in one process)
 struct Switches {
     int rw = 0, kw = 0, s = 0;
-    int smem_cap = 0, max_warps = 0;  // experiment: T81B200_GEMV_LIMITS="shared bytes,consumer warps"
     bool pdl = true, live = false;
     void read_cfg() {
         rw = kw = s = 0;
-        smem_cap = max_warps = 0;
-        if (const char *env = getenv("T81B200_GEMV_LIMITS")) sscanf(env, "%d,%d", &smem_cap, &max_warps);
         if (const char *env = getenv("T81B200_GEMV_CFG")) sscanf(env, "%d,%d,%d", &rw, &kw, &s);
     }
     Switches() {
@@ -751,8 +748,7 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 const int chunks = lps / 4;
                 if (kwv > chunks) continue;                            // a warp without work
                 Plan cand;
-                if (sw.max_warps && rwv * kwv > sw.max_warps) continue;
-                if (!lay_out(cand, key.fmt, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks, sw.smem_cap ? sw.smem_cap : kSmemBudget)) continue;
+                if (!lay_out(cand, key.fmt, planes, key.ntok, tokpad, rwv, kwv, s, lps, chunks, kSmemBudget)) continue;
                 const int rows = 32 * rwv;
                 int64_t row_tiles = 0;
                 for (int i = 0; i < key.n_seg; ++i) row_tiles += (key.M[i] + rows - 1) / rows;
