@@ -23,6 +23,7 @@
 #include "tma.cuh"
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -144,11 +145,13 @@ __device__ __forceinline__ bool epilogue_all(bool pred) {
 // PLANES = 1: bf16 activations as they are.  PLANES = 2: activations split into a bf16 "hi"
 // plane and a bf16 "lo" plane (x = hi + lo to 16 mantissa bits); both are multiplied with the
 // same expanded weights into the same accumulator, on a 128-token tile.
-template <typename CT, int PLANES>
+// NSPLIT = 2 (one plane only): 128-token tiles, for launches whose 256-token tiles would leave most CTAs idle in
+// the last wave; the weight expansion is then done twice as often per flop, so it is only used where it pays.
+template <typename CT, int PLANES, int NSPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ TcOutMaps omaps, const TcParams p) {
-    constexpr int BN = BN_MAX / PLANES;
+    constexpr int BN = BN_MAX / PLANES / NSPLIT;
     constexpr int PLANE_BYTES = BN * BK * 2;
     constexpr uint32_t kInstrDesc = instr_desc(BN);
     extern __shared__ uint8_t smem_raw[];
@@ -209,7 +212,7 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     for (int a = 3 * s; a < 3 * s + 3 && a < p.n_atoms; ++a) {
                         ok = mbar_wait(b_empty(b.stage), b.phase ^ 1);
                         if (!ok) break;
-                        mbar_arrive_expect_tx(b_full(b.stage), B_STAGE_BYTES);
+                        mbar_arrive_expect_tx(b_full(b.stage), PLANES * PLANE_BYTES);
 #pragma unroll
                         for (int pl = 0; pl < PLANES; ++pl)
                             tma_load_2d(b_smem + b.stage * B_STAGE_BYTES + pl * PLANE_BYTES, &map_x, a * BK,
@@ -418,9 +421,9 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
-template <typename CT, int PLANES>
+template <typename CT, int PLANES, int NSPLIT>
 int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcOutMaps &om, const TcParams &p, cudaStream_t st) {
-    auto kern = gemm_trit_tc_kernel<CT, PLANES>;
+    auto kern = gemm_trit_tc_kernel<CT, PLANES, NSPLIT>;
     // the shared-memory limit is a per-device attribute of the function: set it once on every device
     static std::atomic<bool> configured[64];
     int dev = 0;
@@ -437,12 +440,12 @@ int launch_tc(const CUtensorMap &mw, const CUtensorMap &mx, const TcOutMaps &om,
     return T81B200_OK;
 }
 
-template <int PLANES>
+template <int PLANES, int NSPLIT>
 int launch_tc_ct(int c_dtype, const CUtensorMap &mw, const CUtensorMap &mx, const TcOutMaps &om, const TcParams &p, cudaStream_t st) {
     switch (c_dtype) {
-        case T81B200_F32: return launch_tc<float, PLANES>(mw, mx, om, p, st);
-        case T81B200_BF16: return launch_tc<__nv_bfloat16, PLANES>(mw, mx, om, p, st);
-        case T81B200_F16: return launch_tc<__half, PLANES>(mw, mx, om, p, st);
+        case T81B200_F32: return launch_tc<float, PLANES, NSPLIT>(mw, mx, om, p, st);
+        case T81B200_BF16: return launch_tc<__nv_bfloat16, PLANES, NSPLIT>(mw, mx, om, p, st);
+        case T81B200_F16: return launch_tc<__half, PLANES, NSPLIT>(mw, mx, om, p, st);
     }
     return fail(T81B200_EINVAL, "gemm_trit: unknown output dtype %d", c_dtype);
 }
@@ -506,11 +509,21 @@ struct TcPlan {
     size_t scratch_bytes;
 };
 
-TcPlan make_plan(int b_dtype, int layout, int64_t N, int64_t K) {
+TcPlan make_plan(int b_dtype, int layout, int64_t M, int64_t N, int64_t K) {
     TcPlan pl;
     pl.direct = b_dtype == T81B200_BF16 && layout == T81B200_LAYOUT_NK;
     pl.planes = b_dtype == T81B200_BF16 ? 1 : 2;
     pl.bn = BN_MAX / pl.planes;
+    if (pl.planes == 1 && M > 0) {
+        // 128-token tiles only when 256-token tiles would leave more than half of the SMs without any tile: every
+        // tile expands its own 128 x K block of weights, and at 128 tokens the eight converter warps cannot keep
+        // up with the MMAs (measured: 612 instead of 1128 TFLOP/s on 4096 x 4096 x 16384, 470 instead of 627 on
+        // 3072 x 3072 x 2048), so the smaller tile pays only where the extra expansions run on idle SMs
+        // (1024 x 4096 x 1024: 39.5 instead of 42.6 us).  T81B200_TC_TILE_TOKENS=128|256 (read once) forces one.
+        static const int forced = [] { const char *e = getenv("T81B200_TC_TILE_TOKENS"); return e ? atoi(e) : 0; }();
+        const int64_t sms = sm_count(), tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
+        if (forced == 128 || (forced == 0 && tiles256 * 2 <= sms && N > 128)) pl.bn = 128;
+    }
     pl.kpad = (K + 7) & ~(int64_t)7;
     pl.rows_pad = (N + pl.bn - 1) / pl.bn * pl.bn;
     pl.scratch_bytes = pl.direct ? 0 : (size_t)pl.planes * pl.rows_pad * pl.kpad * 2;
@@ -532,7 +545,7 @@ bool gemm_trit_tc_eligible(int b_dtype, int layout, int c_dtype, int64_t M, int6
 
 size_t gemm_trit_tc_workspace(int b_dtype, int layout, int c_dtype, int64_t M, int64_t N, int64_t K) {
     (void)c_dtype; (void)M;
-    return make_plan(b_dtype, layout, N, K).scratch_bytes;
+    return make_plan(b_dtype, layout, 0, N, K).scratch_bytes;
 }
 
 int gemm_trit_tc_status(int reset) {
@@ -549,7 +562,7 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
                         int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M, int64_t N,
                         int64_t K, float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t st,
                         int n_peers, void *const *peer_C) {
-    const TcPlan plan = make_plan(b_dtype, layout, N, K);
+    const TcPlan plan = make_plan(b_dtype, layout, M, N, K);
     const void *x_ptr = B;
     int64_t x_ld = ldb, x_rows = N;
     if (plan.direct) {
@@ -608,7 +621,8 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
         }
         p.n_out_maps = 1 + n_peers;
     }
-    return plan.planes == 2 ? launch_tc_ct<2>(c_dtype, mw, mx, om, p, st) : launch_tc_ct<1>(c_dtype, mw, mx, om, p, st);
+    if (plan.planes == 2) return launch_tc_ct<2, 1>(c_dtype, mw, mx, om, p, st);
+    return plan.bn == 128 ? launch_tc_ct<1, 2>(c_dtype, mw, mx, om, p, st) : launch_tc_ct<1, 1>(c_dtype, mw, mx, om, p, st);
 }
 
 }  // namespace t81b200
