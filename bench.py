@@ -312,6 +312,37 @@ def run_ours(args):
                     else:
                         ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale, C=yd_out[name])
 
+    # N > 1: the decode step with every Linear's rows sharded like the prefill.  Each call multiplies this rank's
+    # rows and stores them into its own result and every peer's (plain stores over NVLink from the kernel), with
+    # no per-call ordering between the ranks: every Linear of a step writes its own rows of a per-name buffer, so
+    # nothing is overwritten inside a step.  The last call of a step carries the flag exchange (its signal is
+    # published after all earlier kernels of the stream have completed), and one wait closes the step: after it
+    # every rank holds every result of the step, before the next step starts.  A consumer chained to a single
+    # Linear would need the flags on that call (about 8 us); the stack's Linears read resident inputs.
+    yd_peer = None
+    if world > 1 and args.decode_shard:
+        from t81lib_b200.nn.sharded import peer_order
+        yd_peer = {name: PeerColumns(dtok * LAYERS, o, torch.bfloat16, dev, copies=1) for name, o, _ in LINEARS}
+        t2_shard = [{m[0]: ops.pack_t2(m[3].contiguous(), m[1], m[2]) for m in mods} for mods in prefill_mods] if use_t2 else None
+
+    def decode_step_sharded():
+        last = LINEARS[-1][0]
+        for li, mods in enumerate(prefill_mods):
+            for name, out_l, in_f, packed, scale in mods:
+                ex = yd_peer[name]
+                lo, hi = rank * out_l, (rank + 1) * out_l
+                rows = slice(li * dtok, (li + 1) * dtok)
+                peers = [ex.peers[r][0][rows, lo:hi] for r in peer_order(rank, world)]
+                closing = li == LAYERS - 1 and name == last
+                with ops.independent_of_previous() if (name in INDEPENDENT and not closing) else contextlib.nullcontext():
+                    if use_t2:
+                        ops.gemm_trit_t2([t2_shard[li][name]], [out_l], xd_in[in_f], K=in_f, row_scales=[scale],
+                                         outs=[ex.buffers[0][rows, lo:hi]], peers=peers, sync=ex.flags if closing else None)
+                    else:
+                        ops.gemm_trit(packed, xd_in[in_f], M=out_l, K=in_f, layout="nk", row_scale=scale,
+                                      C=ex.buffers[0][rows, lo:hi], peers=peers, sync=ex.flags if closing else None)
+        yd_peer[last].flags.wait()
+
     # The same step with the Linears that share an input in ONE launch each (q/k/v, gate/up): 4 launches per
     # block instead of 7, through the additive grouped entry point.  Reported beside the per-Linear figure.
     GROUPS = [("q", "k", "v"), ("o",), ("gate", "up"), ("down",)]
@@ -357,14 +388,14 @@ def run_ours(args):
         torch.cuda.synchronize()
         return g
 
-    graph = capture(decode_step)
+    graph = capture(decode_step_sharded if yd_peer is not None else decode_step)
 
     def decode_all():
         for _ in range(DECODE):
             if graph is not None:
                 graph.replay()
             else:
-                decode_step()
+                (decode_step_sharded if yd_peer is not None else decode_step)()
 
     def barrier():
         if world > 1:
@@ -413,9 +444,15 @@ def run_ours(args):
             "note": "prefill phase: 224 launches per step, includes launch gaps" + ("; includes the exchange" if world > 1 else "")}
     # ---- decode: algorithmic bytes of the streaming kernel (the dominant kernel by time)
     # weight bytes the decode kernel streams: the decode-stream layout (0.25 byte per trit) or the limbs (0.33)
-    limb_bytes = sum(m[3].numel() for mods in layers for m in mods)  # decode runs whole on every rank
-    packed_bytes = sum(t.numel() for d in t2 for t in d.values()) if use_t2 else limb_bytes
-    other_bytes = sum(4 * m[1] + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
+    limb_bytes = sum(m[3].numel() for mods in layers for m in mods)
+    sharded_decode = yd_peer is not None
+    if sharded_decode:  # this rank's rows; its outputs go to world results
+        limb_bytes = limb_bytes // world
+        packed_bytes = sum(t.numel() for d in t2_shard for t in d.values()) if use_t2 else limb_bytes
+        other_bytes = sum(4 * m[1] // world + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
+    else:               # whole on this rank
+        packed_bytes = sum(t.numel() for d in t2 for t in d.values()) if use_t2 else limb_bytes
+        other_bytes = sum(4 * m[1] + 2 * dtok * m[2] + 2 * dtok * m[1] for mods in layers for m in mods)
     bytes_decode = packed_bytes + other_bytes
     n_launch = LAYERS * len(LINEARS)
     gbs = bytes_decode * DECODE / (dec_ms * 1e-3) / 1e9
@@ -426,13 +463,16 @@ def run_ours(args):
             "traffic_note": "bytes per average launch; dram__bytes measured by ncu on one shape equals the algorithmic bytes there",
             "peak_source": pk["source"] + " (copy bandwidth)", "kernel": "gemv_trit_lut_kernel", "tokens": dtok,
             "algorithmic_bytes_per_launch": bytes_decode / n_launch, "us_per_launch": dec_ms * 1e3 / (DECODE * n_launch),
-            "weight_layout": "decode-stream layout (2 bits per trit, made once per weight)" if use_t2 else "packed limbs",
+            "weight_layout": (("decode-stream layout" if use_t2 else "packed limbs") + ", rows sharded over the ranks (per-rank bytes and time)" if sharded_decode else
+                              "decode-stream layout (2 bits per trit, made once per weight)" if use_t2 else "packed limbs"),
             "reference_layout_equivalent": {"bytes_per_launch": (limb_bytes + other_bytes) / n_launch,
                                             "achieved": (limb_bytes + other_bytes) * DECODE / (dec_ms * 1e-3) / 1e9, "unit": "GB/s",
                                             "frac": (limb_bytes + other_bytes) * DECODE / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
                                             "note": "the same time against the bytes the limb layout would have streamed"},
             "cuda_graph": graph is not None, "share_of_step": dec_ms / (pre_ms + dec_ms),
-            "note": "decode phase: 224 launches per step (one per Linear), includes launch gaps" + ("; whole on every rank" if world > 1 else "")}
+            "note": "decode phase: 224 launches per step (one per Linear), includes launch gaps" +
+                    ("; rows sharded, results stored into every rank, one flag exchange per step" if sharded_decode else
+                     "; whole on every rank" if world > 1 else "")}
 
     launches = args.steps * (1 + DECODE) * LAYERS * len(LINEARS)
     line = {
@@ -441,8 +481,9 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "parallelism": (f"prefill: output features of every Linear sharded x{world}, the GEMM epilogue also stores its output block into every peer's "
-                                   f"result over NVLink, flag words order the exchange (no collective); decode: whole on every rank (the exchange "
-                                   f"costs more than the rows saved)") if world > 1 else "single GPU",
+                                   f"result over NVLink, flag words order the exchange (no collective); decode: " +
+                                   ("rows sharded the same way, plain peer stores from the kernel, one flag exchange per step"
+                                    if sharded_decode else "whole on every rank")) if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 2.3 GB of packed weights and a 134 MB activation buffer are streamed each step",
                    "prefill_ms": pre_ms, "decode_ms": dec_ms, "prefill_tokens_per_s": ptok / (pre_ms * 1e-3),
                    "decode_tokens_per_s": dtok * DECODE / (dec_ms * 1e-3)},
@@ -476,6 +517,19 @@ def run_ours(args):
     # ---- N > 1: an un-timed check that the exchange that produced these numbers is right on every rank
     if world > 1:
         line["parity_ok"] = sharded_parity_check(torch, dist, dev, layers, y_peer, world, rank)
+        if yd_peer is not None:
+            # the timed decode steps left every Linear's whole result on every rank: compare the first and the last
+            # block's with the unsharded product computed here (same kernel family; order of the partial sums may
+            # differ with the launch shape: 2^-7 of the largest magnitude, one bf16 rounding)
+            ok = True
+            for li in (0, LAYERS - 1):
+                for name, out_f, in_f, packed, scale in layers[li]:
+                    want = ops.gemm_trit(packed, xd_in[in_f], M=out_f, K=in_f, layout="nk", row_scale=scale).float()
+                    got = yd_peer[name].buffers[0][li * dtok:(li + 1) * dtok].float()
+                    ok = ok and bool((got - want).abs().max() <= 2.0 ** -7 * want.abs().max())
+            flag = torch.tensor([1 if ok else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            line["parity_ok"] = bool(line["parity_ok"] and flag.item() == 1)
 
     if rank == 0:
         line["clocks"] = clocks.summary()
@@ -878,14 +932,23 @@ def run_sweep(args):
             x = torch.randn(tok, k, device=dev, generator=gen).to(torch.bfloat16)
             y = torch.empty(tok, rows, dtype=torch.bfloat16, device=dev)
             n = copies if tok <= 16 else 4
+            use_t2 = tok <= 16 and args.decode_layout == "t2"
+            if use_t2 and t2s is None:
+                t2s = [ops.pack_t2(m[0], rows, k) for m in mats]
+
+            def call(i):
+                m, sc = mats[i % copies]
+                if use_t2:
+                    ops.gemm_trit_t2([t2s[i % copies]], [rows], x, K=k, row_scales=[sc], biases=[bias], outs=[y])
+                else:
+                    ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=sc, bias=bias, C=y)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.stream(stream):
-                ops.gemm_trit(mats[0][0], x, M=rows, K=k, layout="nk", row_scale=mats[0][1], bias=bias, C=y)
+                call(0)
                 torch.cuda.synchronize()
                 with torch.cuda.graph(graph, stream=stream):
                     for i in range(n):
-                        m, sc = mats[i % copies]
-                        ops.gemm_trit(m, x, M=rows, K=k, layout="nk", row_scale=sc, bias=bias, C=y)
+                        call(i)
                 graph.replay()
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -896,8 +959,9 @@ def run_sweep(args):
                 torch.cuda.synchronize()
             sec = e0.elapsed_time(e1) * 1e-3 / (3 * n)
             if tok <= 16:
-                alg = nbytes + 8 * rows + 2 * tok * k + 2 * tok * rows
-                line = {"achieved": alg / sec / 1e9, "unit": "GB/s", "peak": pk["hbm_gbs"], "bound": "hbm"}
+                alg = (t2s[0].numel() if use_t2 else nbytes) + 8 * rows + 2 * tok * k + 2 * tok * rows
+                line = {"achieved": alg / sec / 1e9, "unit": "GB/s", "peak": pk["hbm_gbs"], "bound": "hbm",
+                        "weight_layout": "decode-stream" if use_t2 else "limbs"}
             else:
                 line = {"achieved": 2.0 * rows * k * tok / sec / 1e12, "unit": "TFLOP/s", "peak": pk["bf16_tflops"], "bound": "tensor"}
             line.update({"layer": name, "rows": rows, "k": k, "tokens": tok, "us_per_launch": sec * 1e6,
@@ -914,6 +978,9 @@ def main():
     ap.add_argument("--decode-layout", choices=["t2", "limb"], default="t2",
                     help="weight layout of the decode-sized calls: the decode-stream layout made once per weight (default) "
                          "or the reference's packed limbs")
+    ap.add_argument("--decode-shard", type=int, default=1,
+                    help="N > 1: 1 shards the rows of every decode-sized Linear over the ranks like the prefill (default), "
+                         "0 runs the decode phase whole on every rank")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)

@@ -265,8 +265,12 @@ T81B200_API int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *s
  * reads or writes - e.g. the k and v projections behind q, or up behind gate, which
  * share their input.  The decode-sized kernel then starts its work while its
  * predecessor is still running instead of behind it; it still does not complete before
- * the predecessor has, so later calls can rely on stream order as usual.  Other kernels
- * ignore the hint.  No counterpart in the reference. */
+ * the predecessor has, so later calls can rely on stream order as usual.  A hinted kernel
+ * releases ITS successor at once, so in a run of consecutive hinted calls each one must be
+ * independent of every kernel back to and including the last unhinted one (q, k*, v*: v may
+ * run beside q, not only beside k).  The promise is the caller's; a false one is a data
+ * race the library cannot detect.  Other kernels ignore the hint.  No counterpart in the
+ * reference. */
 T81B200_API void t81b200_hint_independent(int on);
 
 /* Column-block copy for the column-sharded Linear: copies `rows` rows of `width_bytes`
@@ -312,6 +316,12 @@ T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, 
  * No counterpart in the reference (its packed copy per module, t81/nn/linear.py:84-99, is the limb layout). */
 T81B200_API int64_t t81b200_t2_bytes(int64_t rows, int64_t cols);
 T81B200_API int t81b200_pack_t2(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *t2, void *stream);
+/* gemm_trit_t2 for ONE matrix of a column-sharded Linear: t81b200_gemm_trit_peers (see there for peer_C, sync_local
+ * and sync_slots) with the rank's rows given in the decode-stream layout; 1..16 rows of B, token-major. */
+T81B200_API int t81b200_gemm_trit_t2_peers(const uint8_t *t2, const float *row_scale, const float *bias, void *C, int64_t M,
+                                           const void *B, int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N,
+                                           int64_t K, float alpha, float beta, int n_peers, void *const *peer_C,
+                                           uint32_t *sync_local, uint32_t *const *sync_slots, void *stream);
 T81B200_API int t81b200_gemm_trit_t2(int n_group, const uint8_t *const *t2, const float *const *row_scale,
                                      const float *const *bias, void *const *C, const int64_t *M, const void *B,
                                      int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N, int64_t K,

@@ -142,11 +142,8 @@ extern "C" int t81b200_gemm_trit(const uint8_t *A, const float *row_scale, const
                            workspace_bytes, stream, nullptr);
 }
 
-extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
-                                       int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
-                                       int64_t N, int64_t K, float alpha, float beta, void *workspace,
-                                       size_t workspace_bytes, int n_peers, void *const *peer_C, uint32_t *sync_local,
-                                       uint32_t *const *sync_slots, void *stream) {
+// The peers' results and flag slots of a sharded call: present, device memory, reachable from the current GPU.
+static int check_peers(int n_peers, void *const *peer_C, uint32_t *sync_local, uint32_t *const *sync_slots) {
     if (n_peers < 0 || n_peers > T81B200_MAX_PEERS)
         return fail(T81B200_ELIMIT, "gemm_trit_peers: %d peers, at most %d are supported", n_peers, T81B200_MAX_PEERS);
     if (int rc = check_device()) return rc;
@@ -169,6 +166,15 @@ extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale,
             else if (e != cudaSuccess) return fail(T81B200_ECUDA, "gemm_trit_peers: enabling peer access to GPU %d: %s", attr.device, cudaGetErrorString(e));
         }
     }
+    return T81B200_OK;
+}
+
+extern "C" int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
+                                       int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
+                                       int64_t N, int64_t K, float alpha, float beta, void *workspace,
+                                       size_t workspace_bytes, int n_peers, void *const *peer_C, uint32_t *sync_local,
+                                       uint32_t *const *sync_slots, void *stream) {
+    if (int rc = check_peers(n_peers, peer_C, sync_local, sync_slots)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     PeerCtx ctx;
     ctx.n_peers = n_peers; ctx.peer_C = peer_C; ctx.sync_local = sync_local; ctx.sync_slots = sync_slots;
@@ -260,6 +266,26 @@ extern "C" int t81b200_gemm_trit_t2(int n_group, const uint8_t *const *t2, const
     if (N == 0) return T81B200_OK;
     const int rc = gemv_trit_lut_launch(1, n_group, t2, row_scale, bias, C, M, B, b_dtype, ldb, c_dtype, ldc, (int)N, K, alpha, beta,
                                         static_cast<cudaStream_t>(stream), nullptr);
+    if (rc == T81B200_EALIGN) return fail(T81B200_ELIMIT, "gemm_trit_t2: K = %lld does not fit the kernel's shared memory", (long long)K);
+    return rc;
+}
+
+extern "C" int t81b200_gemm_trit_t2_peers(const uint8_t *t2, const float *row_scale, const float *bias, void *C, int64_t M,
+                                          const void *B, int b_dtype, int64_t ldb, int c_dtype, int64_t ldc, int64_t N,
+                                          int64_t K, float alpha, float beta, int n_peers, void *const *peer_C,
+                                          uint32_t *sync_local, uint32_t *const *sync_slots, void *stream) {
+    if (M <= 0 || K <= 0 || N < 0) return fail(T81B200_EINVAL, "gemm_trit_t2_peers: dimensions must be positive");
+    if (N > 16) return fail(T81B200_ELIMIT, "gemm_trit_t2_peers: %lld rows of B; the decode-stream layout serves 1 to 16", (long long)N);
+    if (!valid_dtype(b_dtype) || !valid_dtype(c_dtype)) return fail(T81B200_EINVAL, "gemm_trit: unknown dtype");
+    if (ldb < K || ldc < M) return fail(T81B200_EINVAL, "gemm_trit: leading dimension below the row length");
+    if (N > 0 && (!t2 || !B || !C)) return fail(T81B200_EINVAL, "gemm_trit: null pointer");
+    if (reinterpret_cast<uintptr_t>(t2) % 16 != 0) return fail(T81B200_EALIGN, "gemm_trit_t2: matrices must be 16-byte aligned");
+    if (int rc = check_peers(n_peers, peer_C, sync_local, sync_slots)) return rc;
+    if (N == 0) return T81B200_OK;
+    PeerCtx ctx;
+    ctx.n_peers = n_peers; ctx.peer_C = peer_C; ctx.sync_local = sync_local; ctx.sync_slots = sync_slots;
+    const int rc = gemv_trit_lut_launch(1, 1, &t2, &row_scale, &bias, &C, &M, B, b_dtype, ldb, c_dtype, ldc, (int)N, K, alpha, beta,
+                                        static_cast<cudaStream_t>(stream), &ctx);
     if (rc == T81B200_EALIGN) return fail(T81B200_ELIMIT, "gemm_trit_t2: K = %lld does not fit the kernel's shared memory", (long long)K);
     return rc;
 }

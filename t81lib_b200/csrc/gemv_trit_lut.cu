@@ -551,8 +551,8 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     // token: two 128-bit reads per partial, one 128-bit (16-bit outputs) or two (fp32) stores.
     const int plane = kTokPad * prow;        // floats per K-slice
     const int blocks_per_tok = rows_per_cta / 8;
-    const bool vec_store = p.n_peers == 0 && p.beta == 0.0f && reinterpret_cast<uintptr_t>(S.C) % 16 == 0 &&
-                           (p.ldc * (int64_t)sizeof(CT)) % 16 == 0;
+    bool vec_store = p.beta == 0.0f && reinterpret_cast<uintptr_t>(S.C) % 16 == 0 && (p.ldc * (int64_t)sizeof(CT)) % 16 == 0;
+    for (int pj = 0; pj < p.n_peers; ++pj) vec_store = vec_store && reinterpret_cast<uintptr_t>(p.peer_C[pj]) % 16 == 0;
     auto finish = [&](int tok, int r0, const float (&v)[8]) {  // rows r0 .. r0+7 of the tile, one token
         if (tok >= p.ntok) return;
         float y[8];
@@ -561,12 +561,21 @@ gemv_trit_lut_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
         const int64_t row = cta_row0 + r0;
         CT *c = static_cast<CT *>(S.C) + (int64_t)tok * p.ldc + row;
         if (vec_store && row + 8 <= S.M) {
+            // the same 128-bit stores go into every peer's result (column-sharded Linear), over NVLink
+            const int64_t off = (int64_t)tok * p.ldc + row;
             if constexpr (sizeof(CT) == 4) {
-                reinterpret_cast<float4 *>(c)[0] = make_float4(y[0], y[1], y[2], y[3]);
-                reinterpret_cast<float4 *>(c)[1] = make_float4(y[4], y[5], y[6], y[7]);
+                const float4 lo4 = make_float4(y[0], y[1], y[2], y[3]), hi4 = make_float4(y[4], y[5], y[6], y[7]);
+                reinterpret_cast<float4 *>(c)[0] = lo4;
+                reinterpret_cast<float4 *>(c)[1] = hi4;
+                for (int pj = 0; pj < p.n_peers; ++pj) {
+                    float4 *pc = reinterpret_cast<float4 *>(static_cast<CT *>(p.peer_C[pj]) + off);
+                    pc[0] = lo4; pc[1] = hi4;
+                }
             } else {
-                *reinterpret_cast<uint4 *>(c) = make_uint4(pack_pair<CT>(y[0], y[1]), pack_pair<CT>(y[2], y[3]),
-                                                           pack_pair<CT>(y[4], y[5]), pack_pair<CT>(y[6], y[7]));
+                const uint4 v16 = make_uint4(pack_pair<CT>(y[0], y[1]), pack_pair<CT>(y[2], y[3]),
+                                             pack_pair<CT>(y[4], y[5]), pack_pair<CT>(y[6], y[7]));
+                *reinterpret_cast<uint4 *>(c) = v16;
+                for (int pj = 0; pj < p.n_peers; ++pj) *reinterpret_cast<uint4 *>(static_cast<CT *>(p.peer_C[pj]) + off) = v16;
             }
             return;
         }

@@ -67,7 +67,9 @@ def independent_of_previous():
     """While active, every ``gemm_trit`` call issued by this thread promises that it reads nothing the
     previous kernel on its stream wrote and writes nothing that kernel touches (k and v behind q, up
     behind gate: same input, different outputs).  Decode-sized calls then start while their
-    predecessor still runs; completion order is unchanged, so later calls need no extra care."""
+    predecessor still runs; completion order is unchanged, so later calls need no extra care.
+    A hinted kernel lets its own successor start at once, so in a run of consecutive hinted calls
+    each must be independent of every kernel back to and including the last unhinted one."""
     _capi.lib.t81b200_hint_independent(1)
     try:
         yield
@@ -230,9 +232,36 @@ def pack_t2(packed: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
 
 
 def gemm_trit_t2(t2, rows, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
-                 out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0):
+                 out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0, peers=None, sync=None):
     """``gemm_trit_grouped`` on matrices in the decode-stream layout: ``t2`` is a list of ``pack_t2`` results,
-    ``rows`` their row counts, ``x`` (1..16 tokens, K).  One kernel launch."""
+    ``rows`` their row counts, ``x`` (1..16 tokens, K).  One kernel launch.  ``peers`` / ``sync`` (one matrix
+    only, ``outs`` given): as in ``gemm_trit`` — the result is also stored into the peers' tensors."""
+    if peers:
+        if len(t2) != 1 or outs is None:
+            raise ValueError("peer stores take one matrix and an explicit result tensor")
+        _require_cuda(x, "x")
+        if x.ndim != 2 or x.shape[1] != K or not 1 <= x.shape[0] <= 16:
+            raise ValueError("the decode-stream layout serves 1 to 16 tokens of width K")
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        C, dev, tokens, M = outs[0], x.device, x.shape[0], int(rows[0])
+        if tuple(C.shape) != (tokens, M) or C.stride(1) != 1:
+            raise ValueError("the result must be (tokens, rows) with unit column stride")
+        for t in peers:
+            if tuple(t.shape) != tuple(C.shape) or t.stride() != C.stride() or t.dtype != C.dtype:
+                raise ValueError("peer results must have the local result's shape, strides and dtype")
+        f32 = lambda t: None if t is None else t.detach().to(device=dev, dtype=torch.float32).contiguous()  # noqa: E731
+        scale = f32(row_scales[0]) if row_scales else None
+        bias = f32(biases[0]) if biases else None
+        ptrs = (ctypes.c_void_p * len(peers))(*[t.data_ptr() for t in peers])
+        ldb = x.stride(0) if tokens > 1 else max(K, 1)
+        ldc = C.stride(0) if tokens > 1 else max(M, 1)
+        with torch.cuda.device(dev):
+            _capi.check(_capi.lib.t81b200_gemm_trit_t2_peers(
+                _ptr(t2[0]), _ptr(scale), _ptr(bias), _ptr(C), M, _ptr(x), _dtype_code(x, "x"), ldb, _dtype_code(C, "out"), ldc,
+                tokens, K, float(alpha), float(beta), len(peers), ptrs, None if sync is None else sync.local_ptr,
+                None if sync is None else sync.slot_ptrs, _stream(dev)))
+        return outs
     return gemm_trit_grouped(t2, x, K=K, row_scales=row_scales, biases=biases, outs=outs, out_dtype=out_dtype,
                              alpha=alpha, beta=beta, _t2_rows=[int(r) for r in rows])
 
