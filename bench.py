@@ -612,6 +612,18 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
                     keep.append(y)
         return y
 
+    def run_sharded_step(x):
+        # decode-sized calls through the step-ordered exchange of the sharded modules: no ordering between the
+        # ranks per call, one signal + wait closes the step
+        y = None
+        with torch.no_grad():
+            for row in sharded:
+                for (name, out_f, in_f), m in zip(LINEARS, row):
+                    with ops.independent_of_previous() if name in INDEPENDENT else contextlib.nullcontext():
+                        y = m(x[in_f])
+        ShardedLinear.close_step(dev)
+        return y
+
     def forward(host, out_host):
         x = {w: host[w].to(dev, non_blocking=True) for w in host}
         if sharded is None:
@@ -630,12 +642,18 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
     # memory and its result back out.
     x_static = {w: torch.zeros(dtok, w, dtype=torch.bfloat16, device=dev) for w in (HIDDEN, FFN)}
     stream = torch.cuda.Stream(device=dev)
+    step_sharded = sharded is not None and bool(getattr(args, "decode_shard", 1))
+    if step_sharded:
+        for row in sharded:
+            for m in row:
+                m.step_ordered = True
+    decode_pass = run_sharded_step if step_sharded else run_modules
     with torch.cuda.stream(stream):
-        run_modules(x_static)
+        decode_pass(x_static)  # also builds the per-layer result buffers (collective) before the capture
         torch.cuda.synchronize()
         dgraph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(dgraph, stream=stream):
-            y_static = run_modules(x_static)
+            y_static = decode_pass(x_static)
     torch.cuda.synchronize()
 
     def decode_forward():
@@ -667,7 +685,9 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
     h2d = 2 * (ptok + DECODE * dtok) * (HIDDEN + FFN)
     d2h = 2 * (ptok + DECODE * dtok) * HIDDEN
     return {"value": BATCH * (PREFILL + DECODE) / sec, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": d2h, "steps": steps, "api": ("t81lib_b200.nn.Linear.forward" if world == 1 else "t81lib_b200.nn.sharded.ShardedLinear.forward (prefill, exchange='p2p') + t81lib_b200.nn.Linear.forward (decode)")
+            "d2h_bytes_per_step": d2h, "steps": steps, "api": ("t81lib_b200.nn.Linear.forward" if world == 1 else
+                                                                    "t81lib_b200.nn.sharded.ShardedLinear.forward (prefill: exchange='p2p'; decode: " +
+                                                                    ("step_ordered + close_step" if step_sharded else "whole-matrix t81lib_b200.nn.Linear on every rank") + ")")
                    + " (prefill eager; decode pass replayed from a torch.cuda.CUDAGraph); host copies on every rank"}
 
 

@@ -258,6 +258,11 @@ T81B200_API int t81b200_gemm_trit_peers(const uint8_t *A, const float *row_scale
                             size_t workspace_bytes, int n_peers, void *const *peer_C, uint32_t *sync_local,
                             uint32_t *const *sync_slots, void *stream);
 T81B200_API int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *stream);
+/* The other half, alone: queues, on `stream`, a one-thread kernel that — once everything queued before it on the
+ * stream has completed — publishes one more exchange of this rank to every peer.  Calls issued WITHOUT flags
+ * (sync_local == NULL) into buffers that no other call of the same step writes can thus be closed by one
+ * signal + one wait per step on every rank instead of a wait and a signal per call. */
+T81B200_API int t81b200_exchange_signal(uint32_t *sync_local, uint32_t *const *sync_slots, int n_peers, void *stream);
 
 /* Scheduling hint for the calling thread, in force until changed: while it is on, each
  * t81b200_gemm_trit call promises that it reads nothing (activations, bias, scales) that

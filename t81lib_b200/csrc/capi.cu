@@ -197,6 +197,14 @@ namespace t81b200 { extern thread_local int g_hint_independent; }
 
 extern "C" void t81b200_hint_independent(int on) { t81b200::g_hint_independent = on ? 1 : 0; }
 
+extern "C" int t81b200_exchange_signal(uint32_t *sync_local, uint32_t *const *sync_slots, int n_peers, void *stream) {
+    if (int rc = check_device()) return rc;
+    if (!sync_local || !sync_slots || n_peers < 0 || n_peers > T81B200_MAX_PEERS) return fail(T81B200_EINVAL, "exchange_signal: bad arguments");
+    for (int i = 0; i < n_peers; ++i)
+        if (!sync_slots[i]) return fail(T81B200_EINVAL, "exchange_signal: null flag slot");
+    return exchange_signal_launch(sync_local, sync_slots, n_peers, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *stream) {
     if (int rc = check_device()) return rc;
     if (!sync_local || n_peers < 0 || n_peers > T81B200_MAX_PEERS) return fail(T81B200_EINVAL, "exchange_wait: bad arguments");

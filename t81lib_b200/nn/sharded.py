@@ -102,6 +102,14 @@ class ExchangeFlags:
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
+    def signal(self) -> None:
+        """Queue, on torch's current stream, the publication of one more exchange of this rank: once everything
+        queued before it has completed, the peers' next ``wait`` sees it.  Closes a step of calls issued
+        without flags (``ShardedLinear.step_ordered``)."""
+        from .. import _capi
+        _capi.check(_capi.lib.t81b200_exchange_signal(self.local_ptr, self.slot_ptrs, self.n_peers,
+                                                      torch.cuda.current_stream(self.device).cuda_stream))
+
     def wait(self) -> None:
         """Queue, on torch's current stream, the wait after which everything the peers stored for
         the calls issued so far is in this GPU's memory."""
@@ -204,6 +212,14 @@ class ShardedLinear(nn.Module):
         # p2p only: True leaves the wait for the peers' blocks to the consumer — the next sharded matmul
         # waits at its start by itself; anything else calls ExchangeFlags.wait() first
         self.defer_wait = False
+        # p2p only: True sends decode-sized calls (at most 16 tokens) through the step-ordered exchange — the call
+        # multiplies this rank's rows (decode-stream layout) and stores them into a result buffer of ITS OWN on
+        # every rank, with no ordering between the ranks per call; ``ShardedLinear.close_step(device)`` — one
+        # signal and one wait per rank — then makes every result of the step whole on every rank.  For steps
+        # whose Linears do not consume each other's results before the step is closed; a result is overwritten by
+        # the layer's next call with that token count.
+        self.step_ordered = False
+        self._step_buffers: dict = {}
         self._full_matmul = None
         self._full_bias = None if bias is None or shard_min_tokens <= 0 else bias.detach().clone()
         # `quantize` / `matmul` are injection points for host-side tests of the sharding
@@ -269,9 +285,36 @@ class ShardedLinear(nn.Module):
             ex = ShardedLinear._shared_exchanges[key] = PeerColumns(tokens, self.out_features, dtype, device, self.group)
         return ex
 
+    @staticmethod
+    def close_step(device: torch.device, group=None) -> None:
+        """Queue, on torch's current stream, the end of a step of ``step_ordered`` calls: after it every result
+        returned by those calls is whole on this rank.  Every rank calls it once per step."""
+        flags = ExchangeFlags.get(device, group)
+        flags.signal()
+        flags.wait()
+
+    def _forward_step(self, x: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+        tokens = x.shape[0]
+        ex = self._step_buffers.get((tokens, x.dtype))
+        if ex is None:  # collective: every rank reaches this with the same shape
+            ex = self._step_buffers[(tokens, x.dtype)] = PeerColumns(tokens, self.out_features, x.dtype, x.device, self.group, copies=1)
+        lo, hi = self.rows
+        w = self.ternary_weight
+        if w._t2 is None:
+            w._t2 = ops.pack_t2(w.packed.contiguous(), hi - lo, self.in_features)
+        bias = self.bias
+        if bias is not None and bias.device != x.device:
+            bias = self.bias = bias.to(x.device)
+        ops.gemm_trit_t2([w._t2], [hi - lo], x, K=self.in_features, row_scales=[w.row_scale], biases=[bias],
+                         outs=[ex.buffers[0][:, lo:hi]], peers=ex.peer_blocks(0, lo, hi))
+        return ex.buffers[0]
+
     def _forward_p2p(self, x: torch.Tensor) -> torch.Tensor:
         from .. import ops
         tokens = x.shape[0]
+        if self.step_ordered and 1 <= tokens <= 16:
+            return self._forward_step(x)
         ex = self.exchange_for(tokens, x.dtype, x.device)
         i = ex.next_index()
         lo, hi = self.rows

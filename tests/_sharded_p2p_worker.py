@@ -68,6 +68,30 @@ def main() -> int:
         layer.exchange_for(8, torch.bfloat16, dev).flags.wait()
         torch.cuda.synchronize()
         ok = ok and torch.equal(total, want_sum)
+    # Step-ordered exchange: decode-sized calls store into every rank without per-call ordering, one signal + one
+    # wait per rank closes the step.  Two layers, three steps; results against the unsharded product on the
+    # decode-stream layout (same kernel, other launch shape: one rounding of the output type).
+    from t81lib_b200 import ops
+    w2 = torch.randn(768, 520, generator=gen, device=dev) * 0.02
+    full2 = t81_torch.TernaryTensor.from_float(w2, threshold=0.45, rule="absmean")
+    l1 = ShardedLinear(w, b, threshold=0.45, rule="absmean", exchange="p2p")
+    l2 = ShardedLinear(w2, None, threshold=0.45, rule="absmean", exchange="p2p")
+    l1.step_ordered = l2.step_ordered = True
+    for tokens, dtype in ((8, torch.bfloat16), (3, torch.float32), (16, torch.float16)):
+        for _ in range(3):
+            xs = torch.randn(tokens, 520, generator=gen, device=dev).to(dtype)
+            y1, y2 = l1(xs), l2(xs)
+            ShardedLinear.close_step(dev)
+            torch.cuda.synchronize()
+            want1 = ops.gemm_trit_t2([ops.pack_t2(full.packed, 1024, 520)], [1024], xs, K=520, row_scales=[full.row_scale], biases=[b])[0]
+            want2 = ops.gemm_trit_t2([ops.pack_t2(full2.packed, 768, 520)], [768], xs, K=520, row_scales=[full2.row_scale])[0]
+            for got, want in ((y1, want1), (y2, want2)):
+                tol = (2.0 ** -7 if dtype != torch.float32 else 1e-5) * float(want.float().abs().max())
+                same = float((got.float() - want.float()).abs().max()) <= tol
+                ok = ok and same
+                if rank == 0 and not same:
+                    print(f"STEP MISMATCH tokens={tokens} dtype={dtype}", flush=True)
+            dist.barrier()  # nobody starts the next step's stores before every rank has compared
     ok = ok and _capi.kernel_status(reset=True) == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
