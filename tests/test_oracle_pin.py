@@ -135,6 +135,25 @@ def test_against_compiled_reference_on_random_inputs():
     np.testing.assert_allclose(oracle.gemm_limb(A, B, C0, M, N, KL * 48, 0.75, -1.5), C, rtol=2e-7)
 
 
+@pytest.mark.skipif(not oracle_ref.available(), reason="oracle/_ref not built (reference sources absent)")
+def test_trit_mode_oracle_against_the_reference_sparse_product():
+    """TRIT mode has no dense counterpart in the reference; its sparse helper computes the same product from
+    one COO entry per non-zero trit (include/t81/sparse/simple.hpp:37-94).  It rounds to fp32 after every
+    addition, the oracle accumulates in fp64: agreement to accumulated fp32 rounding."""
+    t81lib = oracle_ref.load()
+    rng = np.random.default_rng(21)
+    for M, K, N, alpha, beta in ((7, 48, 5, 1.0, 0.0), (33, 130, 9, 0.75, -1.5), (64, 1000, 16, 1.0, 0.5)):
+        trits = rng.integers(-1, 2, (M, K)).astype(np.int8)
+        B = rng.normal(size=(K, N)).astype(np.float32)
+        C0 = rng.normal(size=(M, N)).astype(np.float32)
+        r, c = np.nonzero(trits)
+        C = C0.copy()
+        t81lib.spmm_simple([int(v) for v in trits[r, c]], r.astype(np.int32).tolist(), c.astype(np.int32).tolist(),
+                           M, K, B, C, N, alpha, beta)
+        got = oracle.gemm_trit(oracle.pack_trits_rowwise(trits), B, C0, M, N, K, alpha, beta)
+        np.testing.assert_allclose(got, C, rtol=1e-4, atol=1e-4 * float(np.abs(C).max()))
+
+
 def test_elementwise_restatements_match_the_compiled_reference():
     """where / clamp / lerp / addcmul against the reference's CPU code (src/linalg/gemm_dispatch.cpp:147-222)
     compiled from its sources.  The generic build evaluates one float32 operation per operator and must
