@@ -661,6 +661,8 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
             x_static[w].copy_(host_d[w], non_blocking=True)
         dgraph.replay()
         out_d.copy_(y_static, non_blocking=True)
+        if step_sharded:
+            ShardedLinear.release_step(dev)  # the peers' next step overwrites y_static: not before this copy has read it
 
     def job():
         forward(host_p, out_p)

@@ -293,6 +293,14 @@ class ShardedLinear(nn.Module):
         flags.signal()
         flags.wait()
 
+    @staticmethod
+    def release_step(device: torch.device, group=None) -> None:
+        """Queue, on torch's current stream, the point after which the results of the closed step may be overwritten:
+        the same signal + wait, issued by every rank AFTER the work that reads those results has been queued.  A
+        faster rank's next step stores into this rank's result buffers, so a step is: calls, ``close_step``, readers,
+        ``release_step``.  Not needed when nothing reads the results between two steps."""
+        ShardedLinear.close_step(device, group)
+
     def _forward_step(self, x: torch.Tensor) -> torch.Tensor:
         from .. import ops
         tokens = x.shape[0]
