@@ -770,17 +770,18 @@ int make_plan(Plan &pl, const PlanKey &key) {
                 const double wave_ctas = s == 1 ? sms : (s == 2 ? sms - 8 : (s == 4 ? sms - 20 : sms - 36));
                 const double waves = ceil((double)row_tiles * s / wave_ctas);
                 const double warps_per_sched = rwv * kwv / 4.0;
-                const double chunks_per_warp = 0.3 * ceil((double)chunks / kwv) + 0.7 * (double)chunks / kwv;
-                // The decode-stream layout has its own fit (mean regret 4 % over the same sweep): a chunk costs a
-                // warp half as much (no table look-ups), two warps per scheduler already saturate it, the
-                // activations arrive faster relative to the work, half of the shorter bound is not hidden, and
-                // the cluster fold is cheap.
+                // The decode-stream layout has its own fit (mean regret 6 % over the same sweep plus the per-rank
+                // shapes of 2, 4 and 8 GPUs): two warps per scheduler already saturate it, the activation fetch
+                // weighs more (2 TB/s), half of the shorter bound is not hidden, the cluster fold is cheap, and
+                // whole chunks per warp count for more.
                 const bool t2 = key.fmt == 1;
-                const double per_chunk = t2 ? 0.3e-6 : 0.6e-6, sched_cap = t2 ? 2.0 : 3.0;
+                const double whole = t2 ? 0.6 : 0.3;
+                const double chunks_per_warp = whole * ceil((double)chunks / kwv) + (1.0 - whole) * (double)chunks / kwv;
+                const double per_chunk = 0.6e-6, sched_cap = t2 ? 2.0 : 3.0;
                 const double work = chunks_per_warp * per_chunk * (1.0 + 0.4 * (planes * (tokpad / 8) - 1)) *
                                     (warps_per_sched > sched_cap ? warps_per_sched / sched_cap : 1.0);
-                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / (t2 ? 8.0e12 : 5.0e12);
-                const double fold = t2 ? (s == 2 ? 0.3e-6 : (s == 8 ? 0.3e-6 : 0.0))
+                const double x_fetch = (double)row_tiles * s * planes * key.ntok * lps * 96.0 / (t2 ? 2.0e12 : 5.0e12);
+                const double fold = t2 ? (s == 8 ? 0.3e-6 : 0.0)
                                        : (s == 2 ? 0.7e-6 : (s == 4 ? 0.5e-6 : (s == 8 ? 0.8e-6 : 0.0)));
                 const double hidden = t2 ? 0.5 : 0.2;
                 const double t = waves * (1.5e-6 + fold + (work > x_fetch ? work + hidden * x_fetch : x_fetch + hidden * work));
