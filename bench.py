@@ -625,17 +625,28 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
         return y
 
     def forward(host, out_host):
-        x = {w: host[w].to(dev, non_blocking=True) for w in host}
         if sharded is None:
+            x = {w: host[w].to(dev, non_blocking=True) for w in host}
             out_host.copy_(run_modules(x), non_blocking=True)
             return
+        # N > 1: the prefill activations (0.6 GB) enter through rank 0's host copy and reach the other ranks over
+        # NVLink; the result leaves through rank 0.  Eight ranks copying the same bytes from the same host memory
+        # at once take longer than the whole prefill.
+        import torch.distributed as dist
+        if rank == 0:
+            x = {w: host[w].to(dev, non_blocking=True) for w in host}
+        else:
+            x = {w: torch.empty(host[w].shape, dtype=host[w].dtype, device=dev) for w in host}
+        for w in sorted(x):
+            dist.broadcast(x[w], src=0)
         y = None
         with torch.no_grad():
             for row in sharded:
                 for (name, out_f, in_f), m in zip(LINEARS, row):
                     y = m(x[in_f])
         sharded[-1][-1].exchange_for(y.shape[0], y.dtype, dev).flags.wait()  # the peers' blocks of the last result
-        out_host.copy_(y, non_blocking=True)
+        if rank == 0:
+            out_host.copy_(y, non_blocking=True)
 
     # The decode pass (224 module calls on 8 tokens) is captured once in a CUDA graph, the way an
     # inference server drives nn.Modules: every step still copies its inputs in from pinned host
@@ -690,7 +701,9 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
             "d2h_bytes_per_step": d2h, "steps": steps, "api": ("t81lib_b200.nn.Linear.forward" if world == 1 else
                                                                     "t81lib_b200.nn.sharded.ShardedLinear.forward (prefill: exchange='p2p'; decode: " +
                                                                     ("step_ordered + close_step" if step_sharded else "whole-matrix t81lib_b200.nn.Linear on every rank") + ")")
-                   + " (prefill eager; decode pass replayed from a torch.cuda.CUDAGraph); host copies on every rank"}
+                   + " (prefill eager; decode pass replayed from a torch.cuda.CUDAGraph)" +
+                   ("; prefill activations copied in by rank 0 and broadcast over NVLink, prefill result copied out by rank 0, decode "
+                    "inputs and results copied on every rank" if world > 1 else "")}
 
 
 def sharded_parity_check(torch, dist, dev, layers, y_peer, world, rank):
