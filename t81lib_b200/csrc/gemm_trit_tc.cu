@@ -78,6 +78,8 @@ struct TcParams {
                          // this many tensor maps (the local C first, then the peers'); 0: per-element stores
     int n_peers;         // other GPUs that receive a copy of every output element
     void *peer_C[T81B200_MAX_PEERS];  // their C, same strides as the local one
+    int c_vec;           // 1: tokens are contiguous in C (the (M, N) argument order) and 16-byte aligned per 32-token block:
+                         // a thread's 32 tokens of one feature are one run of memory, moved with 128-bit accesses
 };
 
 // Tensor maps of the result, for the TMA-store epilogue: [0] the local C, then one per peer.
@@ -310,7 +312,29 @@ gemm_trit_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN_MAX + c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
+                if (row_ok && p.c_vec && (int64_t)n0 + c * 32 + 32 <= p.N) {
+                    // (M, N) argument order: the thread's 32 tokens are contiguous — whole 16-byte pieces, and with
+                    // beta the old values are all fetched before the first store
+                    constexpr int PER = 16 / (int)sizeof(CT);  // elements per 128-bit access
+                    uint4 *dst = reinterpret_cast<uint4 *>(crow + (int64_t)n0 + c * 32);
+                    uint4 old[32 / PER];
+                    if (p.beta != 0.0f) {
+#pragma unroll
+                        for (int q = 0; q < 32 / PER; ++q) old[q] = dst[q];
+                    }
+#pragma unroll
+                    for (int q = 0; q < 32 / PER; ++q) {
+                        CT out[PER];
+                        const CT *was = reinterpret_cast<const CT *>(&old[q]);
+#pragma unroll
+                        for (int e = 0; e < PER; ++e) {
+                            float y = __uint_as_float(v[q * PER + e]) * scale + bias;
+                            if (p.beta != 0.0f) y += p.beta * to_float<CT>(was[e]);
+                            out[e] = from_float<CT>(y);
+                        }
+                        dst[q] = *reinterpret_cast<const uint4 *>(out);
+                    }
+                } else if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int64_t tok = (int64_t)n0 + c * 32 + i;
@@ -602,6 +626,8 @@ int gemm_trit_tc_launch(const uint8_t *A, const float *row_scale, const void *B,
     p.alpha = alpha; p.beta = beta;
     p.n_peers = n_peers;
     for (int i = 0; i < T81B200_MAX_PEERS; ++i) p.peer_C[i] = i < n_peers ? peer_C[i] : nullptr;
+    p.c_vec = layout == T81B200_LAYOUT_KN && n_peers == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0 &&
+                      (ldc * (int64_t)dtype_size(c_dtype)) % 16 == 0 ? 1 : 0;
     // TMA-store epilogue: 16-bit output, token-major C (features contiguous), no read-modify-write, and every
     // result 16-byte aligned with a 16-byte multiple as its row pitch
     TcOutMaps om;
