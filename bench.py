@@ -601,16 +601,22 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
     out_p = torch.empty(ptok, HIDDEN, dtype=torch.bfloat16).pin_memory()
     out_d = torch.empty(dtok, HIDDEN, dtype=torch.bfloat16).pin_memory()
 
-    def run_modules(x):
+    def run_modules(x, ready=None):
+        # ready: {width: event} — activations still on their way from the host; waited for at their first use
         y = None
+        ready = dict(ready or {})
         with torch.no_grad():
             for row in mods:
                 keep = []  # a block's outputs stay alive together, so k/v (up) never reuse q's (gate's) memory
                 for (name, out_f, in_f), m in zip(LINEARS, row):
+                    if in_f in ready:
+                        torch.cuda.current_stream().wait_event(ready.pop(in_f))
                     with ops.independent_of_previous() if name in INDEPENDENT else contextlib.nullcontext():
                         y = m(x[in_f])
                     keep.append(y)
         return y
+
+    copy_stream = torch.cuda.Stream(device=dev)
 
     def run_sharded_step(x):
         # decode-sized calls through the step-ordered exchange of the sharded modules: no ordering between the
@@ -626,8 +632,17 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
 
     def forward(host, out_host):
         if sharded is None:
-            x = {w: host[w].to(dev, non_blocking=True) for w in host}
-            out_host.copy_(run_modules(x), non_blocking=True)
+            # the first Linears need the HIDDEN-wide activations only: the FFN-wide ones (3.5x the bytes) follow on a
+            # second stream while those Linears run, and the first `down` waits for them
+            main = torch.cuda.current_stream()
+            x = {HIDDEN: host[HIDDEN].to(dev, non_blocking=True)}
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                x[FFN] = host[FFN].to(dev, non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(copy_stream)
+            x[FFN].record_stream(main)
+            out_host.copy_(run_modules(x, {FFN: arrived}), non_blocking=True)
             return
         # N > 1: the prefill activations (0.6 GB) enter through rank 0's host copy and reach the other ranks over
         # NVLink; the result leaves through rank 0.  Eight ranks copying the same bytes from the same host memory
