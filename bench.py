@@ -648,16 +648,26 @@ def e2e_public_api(torch, dev, Linear, layers, args, world=1, rank=0):
         # NVLink; the result leaves through rank 0.  Eight ranks copying the same bytes from the same host memory
         # at once take longer than the whole prefill.
         import torch.distributed as dist
-        if rank == 0:
-            x = {w: host[w].to(dev, non_blocking=True) for w in host}
-        else:
-            x = {w: torch.empty(host[w].shape, dtype=host[w].dtype, device=dev) for w in host}
-        for w in sorted(x):
-            dist.broadcast(x[w], src=0)
+        main = torch.cuda.current_stream()
+
+        def bring(w):  # rank 0's host copy, then the broadcast, on the stream that is current
+            t = host[w].to(dev, non_blocking=True) if rank == 0 else torch.empty(host[w].shape, dtype=host[w].dtype, device=dev)
+            dist.broadcast(t, src=0)
+            return t
+        x = {HIDDEN: bring(HIDDEN)}
+        copy_stream.wait_stream(main)
+        with torch.cuda.stream(copy_stream):  # the FFN-wide activations follow while the first Linears run
+            x[FFN] = bring(FFN)
+            arrived = torch.cuda.Event()
+            arrived.record(copy_stream)
+        x[FFN].record_stream(main)
+        ready = {FFN: arrived}
         y = None
         with torch.no_grad():
             for row in sharded:
                 for (name, out_f, in_f), m in zip(LINEARS, row):
+                    if in_f in ready:
+                        main.wait_event(ready.pop(in_f))
                     y = m(x[in_f])
         sharded[-1][-1].exchange_for(y.shape[0], y.dtype, dev).flags.wait()  # the peers' blocks of the last result
         if rank == 0:
