@@ -104,3 +104,31 @@ def test_t2_grouped_equals_limb_layout_kernel(dev, members, in_f, tokens):
     with pytest.raises(ValueError, match="1 to 16 tokens"):
         ops.gemm_trit_t2(t2, members, torch.zeros(17, in_f, device=dev, dtype=torch.bfloat16), K=in_f)
     assert _capi.kernel_status(reset=True) == 0
+
+
+@pytest_gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_t2_alpha_beta_and_strided_results(dev, dtype):
+    """C = alpha * diag(s) T(A) B + bias + beta * C into a column slice of a wider result (ldc > rows), every
+    output dtype: the per-element epilogue and the 128-bit one."""
+    from t81lib_b200 import _capi, ops
+    rng = np.random.default_rng(3)
+    out_f, in_f, tokens = 200, 520, 5
+    trits = rng.integers(-1, 2, (out_f, in_f)).astype(np.int8)
+    t2 = ops.pack_t2(torch.from_numpy(oracle.pack_trits_rowwise(trits)).to(dev), out_f, in_f)
+    scale = torch.from_numpy(rng.uniform(0.5, 1.5, out_f).astype(np.float32)).to(dev)
+    bias = torch.from_numpy(rng.normal(size=out_f).astype(np.float32)).to(dev)
+    x = torch.from_numpy(rng.normal(size=(tokens, in_f)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    wide = torch.from_numpy(rng.normal(size=(tokens, out_f + 56)).astype(np.float32)).to(dev).to(dtype)
+    before = wide.clone()
+    for beta in (0.0, -0.75):
+        wide.copy_(before)
+        ops.gemm_trit_t2([t2], [out_f], x, K=in_f, row_scales=[scale], biases=[bias], outs=[wide[:, 8:8 + out_f]], alpha=1.5, beta=beta)
+        want = 1.5 * (x.float().cpu().numpy().astype(np.float64) @ trits.T) * scale.cpu().numpy() + bias.cpu().numpy()
+        want = want + beta * before[:, 8:8 + out_f].float().cpu().numpy()
+        got = wide[:, 8:8 + out_f].float().cpu().numpy()
+        tol = 2e-5 if dtype == torch.float32 else 2.0 ** -7
+        assert np.max(np.abs(got - want)) <= tol * np.max(np.abs(want))
+        # nothing outside the slice was touched
+        assert torch.equal(wide[:, :8], before[:, :8]) and torch.equal(wide[:, 8 + out_f:], before[:, 8 + out_f:])
+    assert _capi.kernel_status(reset=True) == 0
