@@ -231,6 +231,33 @@ def pack_t2(packed: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
     return out
 
 
+def gemm_trit_t2_one(t2: torch.Tensor, M: int, x: torch.Tensor, K: int, row_scale: Optional[torch.Tensor] = None,
+                     bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``gemm_trit_t2`` for one matrix with as little host work as the call allows (the kernel runs a few
+    microseconds: list handling and conversions would outweigh it).  ``x`` is (1..16 tokens, K) with unit column
+    stride on ``t2``'s device; ``row_scale`` and ``bias`` are contiguous float32 on that device or None."""
+    tokens = x.shape[0]
+    dev = x.device
+    C = torch.empty((tokens, M), dtype=out_dtype or x.dtype, device=dev)
+    vp = ctypes.c_void_p
+    a = vp(t2.data_ptr())
+    c = vp(C.data_ptr())
+    m = ctypes.c_int64(M)
+    rs = None if row_scale is None else ctypes.byref(vp(row_scale.data_ptr()))
+    bs = None if bias is None else ctypes.byref(vp(bias.data_ptr()))
+    args = (1, ctypes.byref(a), rs, bs, ctypes.byref(c), ctypes.byref(m), x.data_ptr(), _DTYPES[x.dtype],
+            x.stride(0) if tokens > 1 else max(K, 1), _DTYPES[C.dtype], M, tokens, K, 1.0, 0.0,
+            torch.cuda.current_stream(dev).cuda_stream)
+    if torch.cuda.current_device() == dev.index:
+        rc = _capi.lib.t81b200_gemm_trit_t2(*args)
+    else:
+        with torch.cuda.device(dev):
+            rc = _capi.lib.t81b200_gemm_trit_t2(*args)
+    if rc:
+        _capi.check(rc)
+    return C
+
+
 def gemm_trit_t2(t2, rows, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
                  out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0, peers=None, sync=None):
     """``gemm_trit_grouped`` on matrices in the decode-stream layout: ``t2`` is a list of ``pack_t2`` results,

@@ -188,8 +188,12 @@ class TernaryTensor(torch.Tensor):
                 if self._t2 is None:
                     self._t2 = ops.pack_t2(self._packed, self._rows, self._k_actual)
                 try:
-                    return ops.gemm_trit_t2([self._t2], [self._rows], input, K=self._k_actual, row_scales=[self._row_scale],
-                                            biases=[bias], out_dtype=out_dtype)[0]
+                    x = input if input.stride(1) == 1 else input.contiguous()
+                    if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                        raise ValueError(f"x must be float32, bfloat16 or float16, got {x.dtype}")
+                    if bias is not None and (bias.dtype != torch.float32 or bias.device != x.device or not bias.is_contiguous()):
+                        bias = bias.detach().to(device=x.device, dtype=torch.float32).contiguous()
+                    return ops.gemm_trit_t2_one(self._t2, self._rows, x, self._k_actual, self._row_scale, bias, out_dtype)
                 except _capi.LimitError:
                     self._t2 = False  # a contraction too long for that kernel: the limb layout serves it
             return ops.gemm_trit(self._packed, input, M=self._rows, K=self._k_actual, layout="nk",
