@@ -1,4 +1,4 @@
-"""Parity of the two matmul kernels at the shapes the benchmark times, through the C ABI.
+"""Parity of the matmul kernels (both weight layouts of the streaming one) at the shapes the benchmark times, through the C ABI.
 
 The launch shape of the streaming (decode) kernel is picked from the row count and the
 contraction length, so small cases do not reach the configurations the large layers run
@@ -33,6 +33,7 @@ def rel_err(got, want):
 
 
 _weights = {}
+_t2 = {}
 
 
 def packed_layer(dev, out_f, in_f):
@@ -80,6 +81,16 @@ def _check_decode(dev, out_f, in_f, tokens):
                                atol=1e-2 * float(np.sqrt(np.mean(want ** 2))))  # bf16 activations: 1e-2
     # every output element, not only the sampled rows, against the fp32 result of the same kernel
     assert float((y16.float() - y32).abs().max()) <= 2.0 ** -8 * float(y32.abs().max())
+    # the same product on the decode-stream layout of the weight (what the benchmark's decode phase and
+    # TernaryTensor.matmul_input run): against the oracle on the sampled rows, and every element against the above
+    t2 = _t2.get((out_f, in_f))
+    if t2 is None:
+        t2 = _t2[(out_f, in_f)] = ops.pack_t2(packed, out_f, in_f)
+    (z32,) = ops.gemm_trit_t2([t2], [out_f], x, K=in_f, row_scales=[scale], biases=[bias], out_dtype=torch.float32)
+    assert rel_err(z32[:, rows].cpu().numpy(), want) < 2e-5
+    assert float((z32 - y32).abs().max()) <= 1e-5 * float(y32.abs().max())
+    (z16,) = ops.gemm_trit_t2([t2], [out_f], x, K=in_f, row_scales=[scale], biases=[bias])
+    assert float((z16.float() - z32).abs().max()) <= 2.0 ** -8 * float(z32.abs().max())
     assert _capi.kernel_status(reset=True) == 0
 
 
