@@ -57,7 +57,8 @@ def test_pack_t2_bytes_match_the_layout_statement(dev, rows, cols):
 
 
 @pytest_gpu
-@pytest.mark.parametrize("out_f,in_f", [(16, 48), (100, 130), (256, 3072), (130, 4096), (384, 8192), (64, 14336), (1000, 1000)])
+@pytest.mark.parametrize("out_f,in_f", [(16, 48), (100, 130), (256, 3072), (130, 4096), (384, 8192), (64, 14336), (1000, 1000),
+                                       (512, 14336), (128, 4096), (1792, 4096)])  # the last three: per-rank shapes of 8 GPUs
 @pytest.mark.parametrize("tokens", [1, 4, 8, 9, 16])
 def test_t2_product_matches_oracle(dev, out_f, in_f, tokens):
     from t81lib_b200 import _capi, ops
