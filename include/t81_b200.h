@@ -316,9 +316,11 @@ T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, 
  * code 01 = +1, 11 = -1, 00 = 0, rows and columns past the matrix 0.
  *   t2_bytes:     size of the layout for a rows x cols matrix (a multiple of 1536), -1 on bad arguments.
  *   pack_t2:      packed limbs (rows, ceil(cols/48), 16) -> T2 (16-byte aligned), on the device.
- *   gemm_trit_t2: t81b200_gemm_trit_grouped with the matrices given in T2, for 1..16 rows of B (T81B200_ELIMIT
- *                 beyond: prefill-sized products take the limb layout).  One launch.
+ *   gemm_trit_t2: t81b200_gemm_trit_grouped with the matrices given in T2, for 1..T81B200_T2_MAX_ROWS rows of B
+ *                 (T81B200_ELIMIT beyond: prefill-sized products take the limb layout).  One launch per 16 rows;
+ *                 the launches of one call overlap.
  * No counterpart in the reference (its packed copy per module, t81/nn/linear.py:84-99, is the limb layout). */
+#define T81B200_T2_MAX_ROWS 64
 T81B200_API int64_t t81b200_t2_bytes(int64_t rows, int64_t cols);
 T81B200_API int t81b200_pack_t2(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *t2, void *stream);
 /* gemm_trit_t2 for ONE matrix of a column-sharded Linear: t81b200_gemm_trit_peers (see there for peer_C, sync_local

@@ -31,6 +31,7 @@ EXPORTS = (
     "t81b200_qat_update_scale", "t81b200_qat_quantize_pack",
 )
 TQ1_0, TQ2_0 = 0, 1
+T2_MAX_TOKENS = 64  # T81B200_T2_MAX_ROWS
 MAX_GROUP = 3       # T81B200_MAX_GROUP
 EW_WHERE, EW_CLAMP, EW_LERP, EW_ADDCMUL = 0, 1, 2, 3
 

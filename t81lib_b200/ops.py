@@ -261,7 +261,7 @@ def gemm_trit_t2_one(t2: torch.Tensor, M: int, x: torch.Tensor, K: int, row_scal
 def gemm_trit_t2(t2, rows, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
                  out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0, peers=None, sync=None):
     """``gemm_trit_grouped`` on matrices in the decode-stream layout: ``t2`` is a list of ``pack_t2`` results,
-    ``rows`` their row counts, ``x`` (1..16 tokens, K).  One kernel launch.  ``peers`` / ``sync`` (one matrix
+    ``rows`` their row counts, ``x`` (1..64 tokens, K).  One kernel launch per 16 tokens.  ``peers`` / ``sync`` (one matrix
     only, ``outs`` given): as in ``gemm_trit`` — the result is also stored into the peers' tensors."""
     if peers:
         if len(t2) != 1 or outs is None:
@@ -310,8 +310,8 @@ def gemm_trit_grouped(packed, x: torch.Tensor, *, K: int, row_scales=None, biase
     rows = _t2_rows if _t2_rows is not None else [int(p.shape[0]) for p in packed]
     for p in packed:
         _require_cuda(p, "packed")
-    if _t2_rows is not None and not 1 <= tokens <= 16:
-        raise ValueError("the decode-stream layout serves 1 to 16 tokens")
+    if _t2_rows is not None and not 1 <= tokens <= _capi.T2_MAX_TOKENS:
+        raise ValueError(f"the decode-stream layout serves 1 to {_capi.T2_MAX_TOKENS} tokens")
     if outs is None:
         if beta != 0.0:
             raise ValueError("beta != 0 needs outs")
