@@ -318,10 +318,16 @@ T81B200_API int t81b200_gemm_trit_grouped(int n_group, const uint8_t *const *A, 
  *   pack_t2:      packed limbs (rows, ceil(cols/48), 16) -> T2 (16-byte aligned), on the device.
  *   gemm_trit_t2: t81b200_gemm_trit_grouped with the matrices given in T2, for 1..T81B200_T2_MAX_ROWS rows of B
  *                 (T81B200_ELIMIT beyond: prefill-sized products take the limb layout).  One launch per 16 rows;
- *                 the launches of one call overlap.
+ *                 the launches of one call overlap.  Beyond 16 rows t81b200_prefers_streaming says whether this
+ *                 beats t81b200_gemm_trit on the limbs.
  * No counterpart in the reference (its packed copy per module, t81/nn/linear.py:84-99, is the limb layout). */
-#define T81B200_T2_MAX_ROWS 64
+#define T81B200_T2_MAX_ROWS 128
 T81B200_API int64_t t81b200_t2_bytes(int64_t rows, int64_t cols);
+/* 1 when a product of M output features, N rows of B and contraction length K is served faster by
+ * t81b200_gemm_trit_t2 (N <= 16, or slices of 16 rows) than by the tensor-core kernel's tiles behind
+ * t81b200_gemm_trit — the library's estimate, for a caller that holds both layouts (t81b200_gemm_trit makes the
+ * same choice for the limb layout with the limb layout's cost). */
+T81B200_API int t81b200_prefers_streaming(int64_t M, int64_t N, int64_t K);
 T81B200_API int t81b200_pack_t2(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *t2, void *stream);
 /* gemm_trit_t2 for ONE matrix of a column-sharded Linear: t81b200_gemm_trit_peers (see there for peer_C, sync_local
  * and sync_slots) with the rank's rows given in the decode-stream layout; 1..16 rows of B, token-major. */

@@ -27,11 +27,11 @@ EXPORTS = (
     "t81b200_gemm_trit", "t81b200_gemm_trit_host", "t81b200_gemm_trit_static", "t81b200_gemm_trit_workspace_bytes", "t81b200_kernel_status",
     "t81b200_copy_columns", "t81b200_gemm_trit_peers", "t81b200_exchange_wait", "t81b200_hint_independent",
     "t81b200_gemm_limb_auto", "t81b200_gemm_trit_auto", "t81b200_elementwise", "t81b200_elementwise_auto",
-    "t81b200_release_staging", "t81b200_exchange_signal", "t81b200_gemm_trit_grouped", "t81b200_t2_bytes", "t81b200_pack_t2", "t81b200_gemm_trit_t2", "t81b200_gemm_trit_t2_peers", "t81b200_tq_bytes", "t81b200_packed_to_tq", "t81b200_tq_to_packed",
+    "t81b200_release_staging", "t81b200_exchange_signal", "t81b200_gemm_trit_grouped", "t81b200_t2_bytes", "t81b200_pack_t2", "t81b200_prefers_streaming", "t81b200_gemm_trit_t2", "t81b200_gemm_trit_t2_peers", "t81b200_tq_bytes", "t81b200_packed_to_tq", "t81b200_tq_to_packed",
     "t81b200_qat_update_scale", "t81b200_qat_quantize_pack",
 )
 TQ1_0, TQ2_0 = 0, 1
-T2_MAX_TOKENS = 64  # T81B200_T2_MAX_ROWS
+T2_MAX_TOKENS = 128  # T81B200_T2_MAX_ROWS
 MAX_GROUP = 3       # T81B200_MAX_GROUP
 EW_WHERE, EW_CLAMP, EW_LERP, EW_ADDCMUL = 0, 1, 2, 3
 
@@ -90,6 +90,7 @@ def _load() -> ctypes.CDLL:
                                               ctypes.POINTER(vp), ctypes.POINTER(i64), vp, ci, i64, ci, i64, i64, i64,
                                               f32, f32, vp]
     lib.t81b200_exchange_signal.argtypes = [vp, ctypes.POINTER(vp), ci, vp]
+    lib.t81b200_prefers_streaming.argtypes = [i64, i64, i64]
     lib.t81b200_gemm_trit_t2.argtypes = lib.t81b200_gemm_trit_grouped.argtypes
     lib.t81b200_gemm_trit_t2_peers.argtypes = [vp, vp, vp, vp, i64, vp, ci, i64, ci, i64, i64, i64, f32, f32, ci,
                                                ctypes.POINTER(vp), vp, ctypes.POINTER(vp), vp]

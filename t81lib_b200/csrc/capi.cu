@@ -211,6 +211,23 @@ extern "C" int t81b200_exchange_wait(uint32_t *sync_local, int n_peers, void *st
     return exchange_wait_launch(sync_local, n_peers, static_cast<cudaStream_t>(stream));
 }
 
+// 17 .. T81B200_T2_MAX_ROWS rows of B: slices of the streaming kernel, or tensor-core tiles?  Estimates fitted to
+// measurements on the Llama- and Phi-shaped layers: a slice of 16 rows on the decode-stream layout costs about
+// 1.5 us plus its weight bytes at 1.35 TB/s (overlapping slices included), 1.4 times that on the limbs; the
+// tensor-core kernel runs its 128 x 256 tiles in waves of one per SM at about 8.5 ns per contraction step, whatever
+// part of a tile the rows of B fill.
+static bool streaming_wins(int64_t M, int64_t N, int64_t K, double layout_factor) {
+    if (N <= 16) return true;
+    if (N > T81B200_T2_MAX_ROWS || M <= 0 || K <= 0) return false;
+    const double slices = (double)((N + 15) / 16);
+    const double stream_us = layout_factor * slices * (1.5 + (double)M * (double)K * 0.25 / 1.35e6);
+    const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+    const double waves = (double)((tiles + sm_count() - 1) / sm_count());
+    return stream_us < 5.0 + waves * (double)K * 8.5e-3;
+}
+
+extern "C" int t81b200_prefers_streaming(int64_t M, int64_t N, int64_t K) { return streaming_wins(M, N, K, 1.0) ? 1 : 0; }
+
 static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void *B, int b_dtype, int layout,
                            int64_t ldb, const float *bias, void *C, int c_dtype, int64_t ldc, int64_t M,
                            int64_t N, int64_t K, float alpha, float beta, void *workspace,
@@ -231,11 +248,11 @@ static int gemm_trit_local(const uint8_t *A, const float *row_scale, const void 
 
     if (a_aligned && layout == T81B200_LAYOUT_NK && N <= 16 && K > 0)
         return gemv_trit_launch(A, row_scale, B, b_dtype, ldb, bias, C, c_dtype, ldc, M, (int)N, K, alpha, beta, st, ctx);
-    // 17 to 64 rows of B: one launch of the streaming kernel per 16 rows beats a tensor-core tile that would be three
-    // quarters empty (4096 x 4096 x 32: 10 us instead of 42).  A later slice reads and writes nothing an earlier one
+    // 17 to 128 rows of B: one launch of the streaming kernel per 16 rows often beats tensor-core tiles that would be
+    // mostly empty (4096 x 4096 x 32: 10 us instead of 42); streaming_wins decides.  A later slice reads and writes nothing an earlier one
     // touches and is released by it only once its own input is complete: the slices are flagged independent and
     // overlap.  Not with peers: the exchange protocol counts calls, not slices.
-    if (a_aligned && layout == T81B200_LAYOUT_NK && N <= T81B200_T2_MAX_ROWS && K > 0 && !ctx) {
+    if (a_aligned && layout == T81B200_LAYOUT_NK && K > 0 && !ctx && streaming_wins(M, N, K, 1.4)) {
         const int64_t esz_b = (int64_t)dtype_size(b_dtype), esz_c = (int64_t)dtype_size(c_dtype);
         const int hint = t81b200::g_hint_independent;
         int rc = T81B200_OK;

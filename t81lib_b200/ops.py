@@ -261,7 +261,7 @@ def gemm_trit_t2_one(t2: torch.Tensor, M: int, x: torch.Tensor, K: int, row_scal
 def gemm_trit_t2(t2, rows, x: torch.Tensor, *, K: int, row_scales=None, biases=None, outs=None,
                  out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0, beta: float = 0.0, peers=None, sync=None):
     """``gemm_trit_grouped`` on matrices in the decode-stream layout: ``t2`` is a list of ``pack_t2`` results,
-    ``rows`` their row counts, ``x`` (1..64 tokens, K).  One kernel launch per 16 tokens.  ``peers`` / ``sync`` (one matrix
+    ``rows`` their row counts, ``x`` (1..128 tokens, K).  One kernel launch per 16 tokens.  ``peers`` / ``sync`` (one matrix
     only, ``outs`` given): as in ``gemm_trit`` — the result is also stored into the peers' tensors."""
     if peers:
         if len(t2) != 1 or outs is None:

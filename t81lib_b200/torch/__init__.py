@@ -65,8 +65,6 @@ def _to_device_float(tensor: torch.Tensor) -> torch.Tensor:
 # decode-stream layout (ops.pack_t2), made on first use: 0.25 byte per weight on top of the 0.33 of the limbs.
 # False keeps every product on the limb layout.
 DECODE_STREAM_LAYOUT = True
-# up to this many activation rows (one launch per 16; above it the tensor-core kernel's 256-token tiles pay off)
-DECODE_STREAM_MAX_TOKENS = 64
 
 
 class TernaryTensor(torch.Tensor):
@@ -174,6 +172,10 @@ class TernaryTensor(torch.Tensor):
             w = w * self._row_scale.to(dtype)[:, None]
         return w
 
+    def _streams(self, tokens: int) -> bool:
+        """17..128 activation rows: slices of the streaming kernel or tensor-core tiles (the library's estimate)."""
+        return 16 < tokens <= _capi.T2_MAX_TOKENS and bool(_capi.lib.t81b200_prefers_streaming(self._rows, tokens, self._k_actual))
+
     def matmul_input(self, input: torch.Tensor, bias: Optional[torch.Tensor] = None,
                      out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``input @ W.T (+ bias)`` for activations (tokens, cols) -> (tokens, rows).
@@ -185,7 +187,7 @@ class TernaryTensor(torch.Tensor):
             # inference fast path: no autograd node, no device shuffling — one kernel call
             if input.shape[1] != self._k_actual:
                 raise ValueError("rhs dimension does not match ternary weight width")
-            if DECODE_STREAM_LAYOUT and 1 <= input.shape[0] <= DECODE_STREAM_MAX_TOKENS and self._t2 is not False and self._rows > 0 and self._k_actual > 0:
+            if DECODE_STREAM_LAYOUT and (1 <= input.shape[0] <= 16 or self._streams(input.shape[0])) and self._t2 is not False and self._rows > 0 and self._k_actual > 0:
                 # decode-sized: the weight in the decode-stream layout (made once, a quarter fewer bytes to stream)
                 if self._t2 is None:
                     self._t2 = ops.pack_t2(self._packed, self._rows, self._k_actual)
