@@ -235,6 +235,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # the collectives here are barriers, small reductions and one broadcast: nothing in-switch reduction would
+        # speed up, so NCCL is kept on plain peer transfers (no multicast objects bound to these processes' memory)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     assert _capi.device_available(), _capi.last_error()
     pk = peaks()
