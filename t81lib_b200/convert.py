@@ -71,6 +71,12 @@ def _convert_linear_layer(linear: nn.Module, threshold: float, keep_biases_bf16:
     if pack_now and weight.is_cuda and not weight.is_meta:
         ternary.ternary_weight = t81_torch.TernaryTensor.from_float(weight.detach(), threshold=threshold, rule=rule)
         ternary.ternary_weight._float_source = None  # the module owns the float weight; do not pin a second reference
+        if t81_torch.DECODE_STREAM_LAYOUT:
+            # the decode-stream copy too (0.25 byte per weight), so that the first decode step — possibly inside a
+            # CUDA graph capture — does not have to make it
+            from . import ops
+            tw = ternary.ternary_weight
+            tw._t2 = ops.pack_t2(tw.packed, tw._rows, tw._k_actual)
         stats.packed_on_device += 1
         if release_float:
             # inference-only deployment: the packed bytes (2.67 bits per weight) replace the float weight
